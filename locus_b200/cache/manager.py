@@ -140,7 +140,7 @@ class CacheManager:
         for g in self.groups:
             g.n_pages = n_pages
             if g.spec.window > 0 and self.max_step_tokens > 0:
-                per_request = -(-(g.spec.window + self.max_step_tokens) // page_tokens) + 1
+                per_request = -(-(g.spec.window + self.max_step_tokens) // page_tokens) + 1 + -(-g.spec.keep_first // page_tokens)
                 g.n_pages = min(n_pages, n_state_slots * per_request)
         windows = (ctypes.c_int * max(1, len(self.groups)))(*[g.spec.window for g in self.groups])
         group_pages = (ctypes.c_int * max(1, len(self.groups)))(*[g.n_pages for g in self.groups])
@@ -148,6 +148,9 @@ class CacheManager:
                                                max_seq_tokens)
         if not self._core:
             raise ValueError("the native cache could not be created from these sizes")
+        for g in self.groups:
+            if g.spec.window > 0 and g.spec.keep_first > 0:
+                self._lib.locus_cache_set_keep(self._core, g.gid, g.spec.keep_first)
         assert self._lib.locus_cache_table_width(self._core) == self.table_width
         self.state_slots = _StateSlots(self)
         # (group, page) pairs that a commit or a release made free

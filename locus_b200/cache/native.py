@@ -28,6 +28,7 @@ def lib() -> ctypes.CDLL:
             "locus_pool_release": (c_int, [c_void_p, c_int]),
             "locus_pool_retain": (c_int, [c_void_p, c_int]),
             "locus_cache_new": (c_void_p, [c_int, P_INT, c_int, P_INT, c_int, c_int]),
+            "locus_cache_set_keep": (c_int, [c_void_p, c_int, c_int]),
             "locus_cache_total_pages": (c_int, [c_void_p, c_int]),
             "locus_cache_pages_needed": (c_int, [c_void_p, c_int, c_int, c_int]),
             "locus_cache_delete": (None, [c_void_p]),

@@ -9,6 +9,9 @@
 // Both read K and V through the request's block table, honour an optional window (a query
 // at position p sees keys t with p - window < t <= p; window 0 = all keys) and take any head
 // size that is a multiple of 16 up to 256, any number of heads and any group ratio.
+// A window may keep a request's first tokens in sight (keep_first > 0: keys t < keep_first stay
+// visible to every later query, at their true positions), and the softmax may have a sink (sink != 0:
+// one more term of score 0 and no value in the denominator, p_j = exp(s_j) / (1 + sum exp(s_j))).
 // Cache layout of one layer: [n_pages][2 (K, V)][nkv][page_tokens][hd].
 #include "common.cuh"
 #include "attn_ranges.cuh"
@@ -25,6 +28,7 @@ struct AttnArgs {
     const int* items;         // chunk: [n_items, 2] (segment, first query of the tile within it)
                               // decode: [n_items] segment ids
     int nh, nkv, hd, page_tokens, window;
+    int keep_first, sink;     // see the head of the file
     float scale;
     // decode only
     float* part_o;            // [n_items, nh, max_splits, hd]
@@ -104,12 +108,20 @@ __global__ void __launch_bounds__(128) attn_chunk_kernel(AttnArgs a) {
     for (int i = 0; i < 32; ++i) acc[i] = 0.f;
     __syncthreads();
 
-    for (int tile0 = (t_lo / CHUNK_TK) * CHUNK_TK; tile0 <= t_hi; tile0 += CHUNK_TK) {
+    // kept first tokens in front of the window: their tiles come first, the tiles between them and the window are
+    // skipped (keys in ascending order throughout)
+    const int kept = a.window > 0 ? min(a.keep_first, t_lo) : 0;
+    const int win_tile0 = (t_lo / CHUNK_TK) * CHUNK_TK;
+    for (int tile0 = kept > 0 ? 0 : win_tile0; tile0 <= t_hi; tile0 += CHUNK_TK) {
+        if (tile0 >= kept && tile0 < win_tile0) {
+            tile0 = win_tile0 - CHUNK_TK;
+            continue;
+        }
         for (int i = tid; i < CHUNK_TK * hd; i += 128) {
             const int kj = i / hd, d = i % hd;
             const int t = tile0 + kj;
             float kv = 0.f, vv = 0.f;
-            if (t >= t_lo && t <= t_hi) {
+            if ((t >= t_lo || t < kept) && t <= t_hi) {
                 kv = to_f(kv_row<T>(a, table, t, kvh, 0)[d]);
                 vv = to_f(kv_row<T>(a, table, t, kvh, 1)[d]);
             }
@@ -121,7 +133,7 @@ __global__ void __launch_bounds__(128) attn_chunk_kernel(AttnArgs a) {
             const int qi = i / CHUNK_TK, kj = i % CHUNK_TK;
             const int t = tile0 + kj, p = p0 + qi;
             float s = -INFINITY;
-            if (qi < nq && t <= p && t >= t_lo && (a.window == 0 || t > p - a.window)) {
+            if (qi < nq && t <= p && (a.window == 0 || t > p - a.window || t < a.keep_first)) {
                 float dot = 0.f;
                 const float* qr = qs + qi * hd;
                 const float* kr = ks + kj * (hd + 1);
@@ -167,7 +179,7 @@ __global__ void __launch_bounds__(128) attn_chunk_kernel(AttnArgs a) {
         __syncthreads();
     }
     if (my_q < nq) {
-        const float inv = 1.0f / l_s[my_q];
+        const float inv = 1.0f / (a.sink ? l_s[my_q] + expf(-m_s[my_q]) : l_s[my_q]);
         T* o = static_cast<T*>(a.out) + (static_cast<size_t>(row0 + my_q) * a.nh + h) * hd;
 #pragma unroll
         for (int dd = 0; dd < 32; ++dd) {
@@ -227,8 +239,14 @@ __global__ void __launch_bounds__(128) attn_decode_split_kernel(AttnArgs a) {
     const int p = a.seg_ctx[seg];  // position of the single query
     const int row = a.seg_q0[seg];
     const int t_lo = a.window > 0 ? max(0, p - a.window + 1) : 0;
-    const int k0 = max(t_lo, split * DEC_SPLIT);
-    const int k1 = min(p, (split + 1) * DEC_SPLIT - 1);  // inclusive
+    // splits in front of the window's that hold kept first tokens
+    const int kept = a.window > 0 ? min(a.keep_first, t_lo) : 0;
+    const int s0 = t_lo / DEC_SPLIT;
+    const int n_kept_splits = min(s0, (kept + DEC_SPLIT - 1) / DEC_SPLIT);
+    // (the window's first split may hold kept tokens too: it then starts at its own first key)
+    const int k0 = (split < n_kept_splits || kept > split * DEC_SPLIT) ? split * DEC_SPLIT : max(t_lo, split * DEC_SPLIT);
+    const int k1 = split < n_kept_splits ? min(kept, (split + 1) * DEC_SPLIT) - 1
+                                         : min(p, (split + 1) * DEC_SPLIT - 1);  // inclusive
     const int tid = threadIdx.x;
     const size_t part = (static_cast<size_t>(item) * a.nh + h) * a.max_splits + split;
     // The grid has max_splits blocks per (request, head).  If the caller's max_splits does not reach the split of
@@ -245,8 +263,12 @@ __global__ void __launch_bounds__(128) attn_decode_split_kernel(AttnArgs a) {
     // (in units of 16 elements: rows start at multiples of hd, a multiple of 16, and the pool may hold
     // more than 2^32 elements)
     __shared__ unsigned int krow[DEC_SPLIT];
-    for (int j = tid; j < nk; j += 128)
-        krow[j] = static_cast<unsigned int>((kv_row<T>(a, table, k0 + j, kvh, 0) - static_cast<const T*>(a.pool)) >> 4);
+    // (a key between the kept tokens and the window's start may lie in a page that went back: it stands in for
+    // by the split's first key, which is live, and its score is struck below)
+    for (int j = tid; j < nk; j += 128) {
+        const int t = (k0 + j >= t_lo || k0 + j < kept) ? k0 + j : k0;
+        krow[j] = static_cast<unsigned int>((kv_row<T>(a, table, t, kvh, 0) - static_cast<const T*>(a.pool)) >> 4);
+    }
     const size_t v_off = static_cast<size_t>(a.nkv) * a.page_tokens * hd;  // V row = K row + v_off
     __syncthreads();
     float mx = -INFINITY;
@@ -269,7 +291,8 @@ __global__ void __launch_bounds__(128) attn_decode_split_kernel(AttnArgs a) {
 #pragma unroll
             for (int u = 0; u < VEC; ++u) dot = fmaf(qs[d + u], kv[u], dot);
         }
-        const float s = dot * a.scale;
+        // (a split that holds both kept tokens and the window's start: the keys between them count for nothing)
+        const float s = (k0 + j >= t_lo || k0 + j < kept) ? dot * a.scale : -INFINITY;
         sc[j] = s;
         mx = fmaxf(mx, s);
     }
@@ -334,14 +357,14 @@ __global__ void __launch_bounds__(128) attn_decode_split_kernel(AttnArgs a) {
     // The block that finishes last among the splits of this (request, head) merges them: a counter per
     // (request, head), zero before the launch and zero again after it.  The merge adds the splits in
     // ascending order whichever block runs it.
-    const int s0 = t_lo / DEC_SPLIT, s1 = min(p / DEC_SPLIT, a.max_splits - 1);  // the splits that hold keys: all of them count
+    const int s1 = min(p / DEC_SPLIT, a.max_splits - 1);  // the splits that hold keys (kept ones, then s0 .. s1): all of them count
     __shared__ int last_sh;
     __syncthreads();  // every thread's partial results are written ...
     if (tid == 0) {
         __threadfence();  // ... and visible to the other blocks before this block counts itself done
         int* counter = a.counters + static_cast<size_t>(item) * a.nh + h;
         const int done = atomicAdd(counter, 1);
-        last_sh = done == s1 - s0;
+        last_sh = done == s1 - s0 + n_kept_splits;
         if (last_sh) *counter = 0;
     }
     __syncthreads();
@@ -351,29 +374,34 @@ __global__ void __launch_bounds__(128) attn_decode_split_kernel(AttnArgs a) {
     // weight of every split, exp(m_s - M), computed once (threads in parallel) into shared memory
     float* wsplit = red + kpp * hd;  // [s1 - s0 + 1]
     __shared__ float M_sh, inv_sh;
-    const int ns = s1 - s0 + 1;
+    const int ns = s1 - s0 + 1 + n_kept_splits;
+    // the i-th live split, ascending: the kept ones, then s0 .. s1
+    const int skip = s0 - n_kept_splits;
+#define LIVE_SPLIT(i) ((i) < n_kept_splits ? (i) : (i) + skip)
     float mloc = -INFINITY;
-    for (int i = tid; i < ns; i += 128) mloc = fmaxf(mloc, __ldcg(a.part_ml + 2 * (base + s0 + i)));
+    for (int i = tid; i < ns; i += 128) mloc = fmaxf(mloc, __ldcg(a.part_ml + 2 * (base + LIVE_SPLIT(i))));
     mloc = warp_max(mloc);
     if ((tid & 31) == 0) wred[tid >> 5] = mloc;
     __syncthreads();
     if (tid == 0) M_sh = fmaxf(fmaxf(wred[0], wred[1]), fmaxf(wred[2], wred[3]));
     __syncthreads();
     const float M = M_sh;
-    for (int i = tid; i < ns; i += 128) wsplit[i] = expf(__ldcg(a.part_ml + 2 * (base + s0 + i)) - M);
+    for (int i = tid; i < ns; i += 128) wsplit[i] = expf(__ldcg(a.part_ml + 2 * (base + LIVE_SPLIT(i))) - M);
     __syncthreads();
     if (tid == 0) {
         float L = 0.f;
-        for (int i = 0; i < ns; ++i) L += __ldcg(a.part_ml + 2 * (base + s0 + i) + 1) * wsplit[i];
+        for (int i = 0; i < ns; ++i) L += __ldcg(a.part_ml + 2 * (base + LIVE_SPLIT(i)) + 1) * wsplit[i];
+        if (a.sink) L += expf(-M);
         inv_sh = 1.0f / L;
     }
     __syncthreads();
     const float inv = inv_sh;
     for (int d = tid; d < hd; d += 128) {
         float o = 0.f;
-        for (int i = 0; i < ns; ++i) o += __ldcg(a.part_o + (base + s0 + i) * hd + d) * wsplit[i];
+        for (int i = 0; i < ns; ++i) o += __ldcg(a.part_o + (base + LIVE_SPLIT(i)) * hd + d) * wsplit[i];
         static_cast<T*>(a.out)[(static_cast<size_t>(row) * a.nh + h) * hd + d] = from_f<T>(o * inv);
     }
+#undef LIVE_SPLIT
 }
 
 // ---------------------------------------------------------------------------
@@ -709,6 +737,7 @@ __global__ void __launch_bounds__(32 * DS_WARPS, DEEP ? 2 : 4) attn_decode_strea
                 o.z = fmaf(v.z, w, o.z);
                 o.w = fmaf(v.w, w, o.w);
             }
+            if (a.sink) L += exp2f(-M);   // scores are in base 2 here
             const float inv = 1.0f / L;
             T* dst = static_cast<T*>(a.out) + (static_cast<size_t>(row) * a.nh + h) * hd + d;
             dst[0] = from_f<T>(o.x * inv);
@@ -735,8 +764,8 @@ extern "C" void locus_attn_decode_set_cost(int range_overhead, int merge_per_ran
     g_ds_cost_merge = merge_per_range;
 }
 
-static int check_common(int nh, int nkv, int hd, int page_tokens, int window) {
-    if (nh <= 0 || nkv <= 0 || nh % nkv != 0) return LOCUS_ERR_UNSUPPORTED;
+static int check_common(int nh, int nkv, int hd, int page_tokens, int window, int keep_first = 0) {
+    if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || keep_first < 0) return LOCUS_ERR_UNSUPPORTED;
     if (hd <= 0 || hd % 16 != 0 || hd > 256) return LOCUS_ERR_UNSUPPORTED;
     if (page_tokens <= 0 || window < 0) return LOCUS_ERR_UNSUPPORTED;
     return 0;
@@ -745,11 +774,12 @@ static int check_common(int nh, int nkv, int hd, int page_tokens, int window) {
 static AttnArgs make_args(const void* q, const void* pool, void* out, const int* seg_q0,
                           const int* seg_qn, const int* seg_ctx, const int* block_table,
                           int table_stride, const int* items, int nh, int nkv, int hd,
-                          int page_tokens, int window, float scale) {
+                          int page_tokens, int window, float scale, int keep_first = 0, int sink = 0) {
     AttnArgs a;
     a.q = q; a.pool = pool; a.out = out; a.seg_q0 = seg_q0; a.seg_qn = seg_qn; a.seg_ctx = seg_ctx;
     a.block_table = block_table; a.table_stride = table_stride; a.items = items; a.nh = nh;
     a.nkv = nkv; a.hd = hd; a.page_tokens = page_tokens; a.window = window; a.scale = scale;
+    a.keep_first = window > 0 ? keep_first : 0; a.sink = sink;
     a.part_o = nullptr; a.part_ml = nullptr; a.counters = nullptr; a.max_splits = 0;
     return a;
 }
@@ -758,12 +788,12 @@ extern "C" int locus_attn_chunk(const void* q, int dt, const void* pool, void* o
                                 const int* seg_q0, const int* seg_qn, const int* seg_ctx,
                                 const int* block_table, int table_stride, const int* items,
                                 int n_items, int nh, int nkv, int hd, int page_tokens, int window,
-                                float scale, cudaStream_t stream) {
+                                float scale, int keep_first, int sink, cudaStream_t stream) {
     if (n_items <= 0) return 0;
-    if (int e = check_common(nh, nkv, hd, page_tokens, window)) return e;
+    if (int e = check_common(nh, nkv, hd, page_tokens, window, keep_first)) return e;
     if (n_items > 65535) return LOCUS_ERR_UNSUPPORTED;
     AttnArgs a = make_args(q, pool, out, seg_q0, seg_qn, seg_ctx, block_table, table_stride, items,
-                           nh, nkv, hd, page_tokens, window, scale);
+                           nh, nkv, hd, page_tokens, window, scale, keep_first, sink);
     const size_t smem = sizeof(float) * (CHUNK_BQ * hd + CHUNK_TK * (hd + 1) + CHUNK_TK * hd +
                                          CHUNK_BQ * (CHUNK_TK + 1) + 3 * CHUNK_BQ);
     dim3 grid(nh, n_items);
@@ -789,12 +819,12 @@ extern "C" int locus_attn_decode(const void* q, int dt, const void* pool, void* 
                                  const int* block_table, int table_stride, const int* items,
                                  int n_items, int nh, int nkv, int hd, int page_tokens, int window,
                                  float scale, float* part_o, float* part_ml, int* counters, int max_splits,
-                                 long long max_units, cudaStream_t stream) {
+                                 long long max_units, int keep_first, int sink, cudaStream_t stream) {
     if (n_items <= 0) return 0;
-    if (int e = check_common(nh, nkv, hd, page_tokens, window)) return e;
+    if (int e = check_common(nh, nkv, hd, page_tokens, window, keep_first)) return e;
     if (nh > 65535 || max_splits <= 0 || max_splits > 65535) return LOCUS_ERR_UNSUPPORTED;
     AttnArgs a = make_args(q, pool, out, seg_q0, seg_qn, seg_ctx, block_table, table_stride, items,
-                           nh, nkv, hd, page_tokens, window, scale);
+                           nh, nkv, hd, page_tokens, window, scale, keep_first, sink);
     a.part_o = part_o; a.part_ml = part_ml; a.counters = counters; a.max_splits = max_splits;
     if (counters == nullptr) return LOCUS_ERR_UNSUPPORTED;
     if (max_units < static_cast<long long>(n_items) * nh) return LOCUS_ERR_UNSUPPORTED;
@@ -803,8 +833,9 @@ extern "C" int locus_attn_decode(const void* q, int dt, const void* pool, void* 
     const int pieces = hd * (dt == LOCUS_DT_F32 ? 4 : 2) / 16;
     const int lpk = pieces < 4 ? 0 : pieces <= 8 ? 8 : pieces <= 16 ? 16 : pieces <= 32 ? 32 : 0;
     const int chunk_keys = lpk > 0 ? DS_LOADS * 32 / lpk : 1;
+    // (a window that keeps first tokens: the split kernel below, whose fixed ranges of positions hold them as they are)
     if ((dt == LOCUS_DT_F32 || dt == LOCUS_DT_BF16) && lpk > 0 && n_items <= DS_MAX_ITEMS &&
-        page_tokens % chunk_keys == 0) {
+        page_tokens % chunk_keys == 0 && a.keep_first == 0) {
         static int n_sm = 0;
         if (n_sm == 0) {
             int dev = 0;
@@ -908,5 +939,5 @@ extern "C" int locus_attn_decode_static(const void* q, int dt, const void* pool,
     // and the counters are zero between calls.
     return locus_attn_decode(q, dt, pool, out, seg_q0, seg_qn, seg_ctx, block_table, table_stride,
                              items, n_items, nh, nkv, hd, page_tokens, window, scale, part_o, part_ml,
-                             g_attn_static_cnt_ptr[dev], max_splits, cap, stream);
+                             g_attn_static_cnt_ptr[dev], max_splits, cap, 0, 0, stream);
 }

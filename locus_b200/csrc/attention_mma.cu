@@ -35,6 +35,7 @@ struct MmaAttnArgs {
     int table_stride;
     const int* items;
     int nh, nkv, page_tokens, window;
+    int keep_first, sink;   // a window that keeps a request's first tokens in sight; one more term of score 0 in the denominator
     float scale;
     int n_splits;     // ranges of key tiles per item (1: the block writes out itself)
     float* part_o;    // [item][head][split][MQ][hd] unnormalised sums
@@ -42,11 +43,18 @@ struct MmaAttnArgs {
 };
 
 // Key tiles of an item: the first tile's first position and their number (the same in both kernels).
-__device__ __forceinline__ void item_tiles(int p0, int nq, int window, int& first_tile, int& n_tiles) {
+// With kept first tokens the tiles that hold them and lie in front of the window's first tile come first
+// (kept_tiles of them, from position 0); tile number i of the item starts at tile_pos(i).
+__device__ __forceinline__ void item_tiles(int p0, int nq, int window, int keep_first, int& first_tile, int& n_tiles,
+                                           int& kept_tiles) {
     const int t_hi = p0 + nq - 1;
     const int t_lo = window > 0 ? max(0, p0 - window + 1) : 0;
     first_tile = (t_lo / MK) * MK;
-    n_tiles = (t_hi - first_tile) / MK + 1;
+    kept_tiles = window > 0 ? min(first_tile / MK, (min(keep_first, t_lo) + MK - 1) / MK) : 0;
+    n_tiles = (t_hi - first_tile) / MK + 1 + kept_tiles;
+}
+__device__ __forceinline__ int tile_pos(int i, int first_tile, int kept_tiles) {
+    return i < kept_tiles ? i * MK : first_tile + (i - kept_tiles) * MK;
 }
 
 __device__ __forceinline__ uint32_t sm_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -107,11 +115,12 @@ __global__ void __launch_bounds__(128) attn_chunk_mma_kernel(MmaAttnArgs a) {
     const float scale_log2 = a.scale * 1.4426950408889634f;
 
     // this block's range of the item's key tiles
-    int first_tile, n_tiles_all;
-    item_tiles(p0, nq, a.window, first_tile, n_tiles_all);
+    int first_tile, n_tiles_all, kept_tiles;
+    item_tiles(p0, nq, a.window, a.keep_first, first_tile, n_tiles_all, kept_tiles);
+    const int kept = a.window > 0 ? min(a.keep_first, t_lo) : 0;
     const int split = blockIdx.z;
     const int per_split = (n_tiles_all + a.n_splits - 1) / a.n_splits;
-    first_tile += split * per_split * MK;
+    const int first_idx = split * per_split;
     const int n_tiles = max(0, min(per_split, n_tiles_all - split * per_split));
     if (n_tiles == 0) return;  // the merge counts the live ranges the same way
 
@@ -129,7 +138,7 @@ __global__ void __launch_bounds__(128) attn_chunk_mma_kernel(MmaAttnArgs a) {
         for (int i = tid; i < MK * CH; i += 128) {
             const int r = i / CH, c = i % CH;
             const int t = tile0 + r;
-            const bool ok = t >= t_lo && t <= t_hi;
+            const bool ok = (t >= t_lo || t < kept) && t <= t_hi;
             const int tt = ok ? t : t_hi;  // any valid position: the copy size is 0 when !ok
             const int page = table[pshift >= 0 ? tt >> pshift : tt / P];
             const int off = pshift >= 0 ? tt & (P - 1) : tt % P;
@@ -142,7 +151,7 @@ __global__ void __launch_bounds__(128) attn_chunk_mma_kernel(MmaAttnArgs a) {
         cp_commit();
     };
 
-    load_kv(first_tile, 0);
+    load_kv(tile_pos(first_idx, first_tile, kept_tiles), 0);
 
     // ---- Q fragments of this warp's 16 rows, kept in registers
     cp_wait<1>();   // the Q group is done (the first K/V group may still fly)
@@ -166,10 +175,10 @@ __global__ void __launch_bounds__(128) attn_chunk_mma_kernel(MmaAttnArgs a) {
     const int pq[2] = {p0 + warp * 16 + g, p0 + warp * 16 + g + 8};  // positions of this lane's two query rows
 
     for (int it = 0; it < n_tiles; ++it) {
-        const int tile0 = first_tile + it * MK;
+        const int tile0 = tile_pos(first_idx + it, first_tile, kept_tiles);
         const int buf = it & 1;
         if (it + 1 < n_tiles) {
-            load_kv(tile0 + MK, buf ^ 1);
+            load_kv(tile_pos(first_idx + it + 1, first_tile, kept_tiles), buf ^ 1);
             cp_wait<1>();
         } else {
             cp_wait<0>();
@@ -213,7 +222,7 @@ __global__ void __launch_bounds__(128) attn_chunk_mma_kernel(MmaAttnArgs a) {
                     const int rr = i >> 1;
                     const int t = tile0 + j * 8 + qd * 2 + (i & 1);
                     const int p = pq[rr];
-                    const bool ok = t <= p && t >= t_lo && (a.window == 0 || t > p - a.window);
+                    const bool ok = t <= p && (a.window == 0 || t > p - a.window || t < a.keep_first);
                     const float v = ok ? s[j][i] * scale_log2 : -INFINITY;
                     s[j][i] = v;
                     mx[rr] = fmaxf(mx[rr], v);
@@ -303,7 +312,7 @@ __global__ void __launch_bounds__(128) attn_chunk_mma_kernel(MmaAttnArgs a) {
     for (int rr = 0; rr < 2; ++rr) {
         const int r = warp * 16 + g + rr * 8;
         if (r >= nq) continue;
-        const float inv = 1.0f / l_run[rr];
+        const float inv = 1.0f / (a.sink ? l_run[rr] + exp2f(-m_run[rr]) : l_run[rr]);   // (scores are in base 2)
         bf16* dst = a.out + (static_cast<size_t>(row0 + r) * a.nh + h) * HD;
 #pragma unroll
         for (int d = 0; d < DT; ++d) {
@@ -326,8 +335,8 @@ __global__ void __launch_bounds__(128) attn_chunk_merge_kernel(MmaAttnArgs a, in
     if (i >= nq * half) return;
     const int r = i / half, d = (i - r * half) * 2;
     const int row0 = a.seg_q0[seg] + qoff;
-    int first_tile, n_tiles;
-    item_tiles(a.seg_ctx[seg] + qoff, nq, a.window, first_tile, n_tiles);
+    int first_tile, n_tiles, kept_tiles;
+    item_tiles(a.seg_ctx[seg] + qoff, nq, a.window, a.keep_first, first_tile, n_tiles, kept_tiles);
     const int per_split = (n_tiles + a.n_splits - 1) / a.n_splits;
     const int live = (n_tiles + per_split - 1) / per_split;
     const size_t unit0 = (static_cast<size_t>(item) * a.nh + h) * a.n_splits;
@@ -352,6 +361,7 @@ __global__ void __launch_bounds__(128) attn_chunk_merge_kernel(MmaAttnArgs a, in
         x += v[s].x * w;
         y += v[s].y * w;
     }
+    if (a.sink) L += exp2f(-M);
     const float inv = 1.0f / L;
     *reinterpret_cast<uint32_t*>(a.out + (static_cast<size_t>(row0 + r) * a.nh + h) * hd + d) = pack_bf16(x * inv, y * inv);
 }
@@ -378,9 +388,11 @@ static int launch(const MmaAttnArgs& a, int n_items, cudaStream_t stream) {
 extern "C" int locus_attn_chunk_mma(const void* q, const void* pool, void* out, const int* seg_q0, const int* seg_qn,
                                     const int* seg_ctx, const int* block_table, int table_stride, const int* items,
                                     int n_items, int nh, int nkv, int hd, int page_tokens, int window, float scale,
-                                    int n_splits, float* part_o, float* part_ml, cudaStream_t stream) {
+                                    int n_splits, float* part_o, float* part_ml, int keep_first, int sink,
+                                    cudaStream_t stream) {
     if (n_items <= 0) return 0;
-    if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || nh > 65535 || page_tokens <= 0 || window < 0) return LOCUS_ERR_UNSUPPORTED;
+    if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || nh > 65535 || page_tokens <= 0 || window < 0 || keep_first < 0)
+        return LOCUS_ERR_UNSUPPORTED;
     if (n_splits < 1 || n_splits > MERGE_MAX_SPLITS || (n_splits > 1 && n_items > 65535) || (n_splits > 1 && (part_o == nullptr || part_ml == nullptr)) ||
         ((reinterpret_cast<uintptr_t>(part_o) | reinterpret_cast<uintptr_t>(part_ml)) & 7))
         return LOCUS_ERR_UNSUPPORTED;
@@ -388,7 +400,7 @@ extern "C" int locus_attn_chunk_mma(const void* q, const void* pool, void* out, 
     a.q = static_cast<const bf16*>(q); a.pool = static_cast<const bf16*>(pool); a.out = static_cast<bf16*>(out);
     a.seg_q0 = seg_q0; a.seg_qn = seg_qn; a.seg_ctx = seg_ctx; a.block_table = block_table;
     a.table_stride = table_stride; a.items = items; a.nh = nh; a.nkv = nkv; a.page_tokens = page_tokens;
-    a.window = window; a.scale = scale;
+    a.window = window; a.scale = scale; a.keep_first = window > 0 ? keep_first : 0; a.sink = sink;
     a.n_splits = n_splits; a.part_o = part_o; a.part_ml = part_ml;
     switch (hd) {
         case 16: return launch<16>(a, n_items, stream);

@@ -6,25 +6,25 @@
 // ---------------------------------------------------------------------------
 // Embedding: out[t, :] = table[tokens[t], :] as float32 (the residual stream is float32).
 __global__ void embed_rows_kernel(const int* __restrict__ tokens, const void* __restrict__ table,
-                                  int table_dt, float* __restrict__ out, int H, int copies) {
+                                  int table_dt, float* __restrict__ out, int H, int copies, float scale) {
     pdl_entry();
     pdl_trigger();
     const int t = blockIdx.x;
     const size_t row = static_cast<size_t>(tokens[t]) * H;
     float* o = out + static_cast<size_t>(t) * H * copies;
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        const float v = ld_dyn(table, table_dt, row + i);
+        const float v = ld_dyn(table, table_dt, row + i) * scale;
         for (int c = 0; c < copies; ++c) o[c * H + i] = v;
     }
 }
 
-// copies > 1: a row of out holds the table's row that many times, one behind the other (a model that keeps
+// scale: a factor on the row (1: none).  copies > 1: a row of out holds the table's row that many times, one behind the other (a model that keeps
 // several copies of the residual stream starts them all from the embedding).
 extern "C" int locus_embed_rows(const int* tokens, const void* table, int table_dt, float* out,
-                                int T, int H, int copies, cudaStream_t stream) {
+                                int T, int H, int copies, float scale, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (copies < 1) return LOCUS_ERR_UNSUPPORTED;
-    locus_launch(embed_rows_kernel, T, 256, 0, stream, tokens, table, table_dt, out, H, copies);
+    locus_launch(embed_rows_kernel, T, 256, 0, stream, tokens, table, table_dt, out, H, copies, scale);
     return locus_launch_status();
 }
 

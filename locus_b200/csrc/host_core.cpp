@@ -64,6 +64,7 @@ inline int pages_of(int tokens, int page_tokens) { return (tokens + page_tokens 
 struct Cache {
     int page_tokens, n_pages, max_seq_tokens, table_width;  // n_pages: of the largest group
     std::vector<int> window;  // per group, 0 = all keys
+    std::vector<int> keep;    // per group with a window: a request's first tokens that stay in sight (their pages never go back)
     std::vector<Pool> pools;
     Pool slots;
     std::vector<Seq> seqs;
@@ -76,6 +77,7 @@ struct Cache {
           table_width(pages_of(max_seq, page_tokens_) > 0 ? pages_of(max_seq, page_tokens_) : 1), slots(n_slots) {
         for (int g = 0; g < n_groups; ++g) {
             window.push_back(windows[g]);
+            keep.push_back(0);
             pools.emplace_back(group_pages[g]);
             n_pages = group_pages[g] > n_pages ? group_pages[g] : n_pages;
         }
@@ -87,7 +89,7 @@ struct Cache {
         const int all = pages_of(n_tokens, page_tokens);
         const int w = window[static_cast<size_t>(g)];
         if (w <= 0 || step_tokens <= 0) return all;
-        const int span = pages_of(w + step_tokens, page_tokens) + 1;
+        const int span = pages_of(w + step_tokens, page_tokens) + 1 + pages_of(keep[static_cast<size_t>(g)], page_tokens);
         return all < span ? all : span;
     }
 
@@ -227,6 +229,15 @@ int locus_cache_ensure(void* cv, int64_t h, int n_more) {
     return 1;
 }
 
+// A group's window keeps every request's first keep_first tokens in sight: their pages never go back.  Set before
+// the first request opens.  0 ok; -1 no such group or a negative count.
+int locus_cache_set_keep(void* cv, int g, int keep_first) {
+    Cache* c = as_cache(cv);
+    if (g < 0 || g >= c->n_groups() || keep_first < 0) return -1;
+    c->keep[static_cast<size_t>(g)] = keep_first;
+    return 0;
+}
+
 // n tokens were written after the cached ones.  In a group with a window, pages that no later
 // query can see go back: a query at position p sees keys t > p - window and the next query is at
 // position n_tokens, so pages wholly below n_tokens - window + 1 are dead.  Writes the (group,
@@ -246,7 +257,8 @@ int locus_cache_commit(void* cv, int64_t h, int n, int* freed, int cap) {
         int dead = (s->n_tokens - w + 1) / c->page_tokens;
         if (s->n_tokens - w + 1 < 0) dead = 0;
         if (dead > static_cast<int>(t.size())) dead = static_cast<int>(t.size());
-        for (int i = 0; i < dead; ++i) {
+        // (the pages that hold a request's kept first tokens stay)
+        for (int i = pages_of(c->keep[static_cast<size_t>(g)], c->page_tokens); i < dead; ++i) {
             if (t[static_cast<size_t>(i)] >= 0) {
                 if (c->pools[static_cast<size_t>(g)].release(t[static_cast<size_t>(i)]) == 1)
                     note_freed(freed, cap, n_freed, g, t[static_cast<size_t>(i)]);

@@ -199,9 +199,9 @@ F = ctypes.c_float
 
 
 # ---------------------------------------------------------------------------
-def embed_rows(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor, copies: int = 1) -> None:
-    """out[t, :] = table[tokens[t], :] as float32; ``copies`` > 1: the row that many times, one behind the other
-    (``out`` [T, copies * H])."""
+def embed_rows(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor, copies: int = 1, scale: float = 1.0) -> None:
+    """out[t, :] = table[tokens[t], :] * scale as float32; ``copies`` > 1: the row that many times, one behind the
+    other (``out`` [T, copies * H])."""
     _i32(tokens, "tokens")
     _cuda_c(table, "table")
     _cuda_c(out, "out")
@@ -209,7 +209,7 @@ def embed_rows(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor, cop
     _need(out.dtype == torch.float32, "embed_rows: out must be float32")
     _need(tokens.numel() == T and copies >= 1 and out.shape[1] == H * copies, "embed_rows: shape mismatch")
     code = _lib("elementwise").locus_embed_rows(
-        _p(tokens), _p(table), I(dtype_code(table.dtype)), _p(out), I(T), I(H), I(copies), _stream()
+        _p(tokens), _p(table), I(dtype_code(table.dtype)), _p(out), I(T), I(H), I(copies), F(scale), _stream()
     )
     _check(code, "embed_rows")
 
@@ -609,9 +609,11 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, inv_freq: Optional
 def attn_chunk(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, *, seg_q0: torch.Tensor,
                seg_qn: torch.Tensor, seg_ctx: torch.Tensor, block_table: torch.Tensor,
                items: torch.Tensor, n_items: int, n_heads: int, n_kv_heads: int, head_dim: int,
-               page_tokens: int, window: int, scale: float) -> None:
+               page_tokens: int, window: int, scale: float, keep_first: int = 0, sink: bool = False) -> None:
     """Attention of portions of prompts: ``items`` [n_items, 2] = (segment, first query of a
-    16-query tile).  Keys come from the cache through ``block_table`` [n_seg, width]."""
+    16-query tile).  Keys come from the cache through ``block_table`` [n_seg, width].  ``keep_first``: with a
+    window, a request's first that many tokens stay in sight of every later query; ``sink``: the softmax has one
+    more term of score 0 and no value in its denominator."""
     _cuda_c(q, "q")
     _cuda_c(out, "out")
     _cuda_c(pool, "pool")
@@ -621,7 +623,7 @@ def attn_chunk(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, *, seg_q0
     code = _lib("attention").locus_attn_chunk(
         _p(q), I(dtype_code(q.dtype)), _p(pool), _p(out), _p(seg_q0), _p(seg_qn), _p(seg_ctx),
         _p(block_table), I(block_table.shape[1]), _p(items), I(n_items), I(n_heads), I(n_kv_heads),
-        I(head_dim), I(page_tokens), I(window), F(scale), _stream()
+        I(head_dim), I(page_tokens), I(window), F(scale), I(keep_first), I(1 if sink else 0), _stream()
     )
     _check(code, "attn_chunk", f"(heads {n_heads}/{n_kv_heads}, head_dim {head_dim})")
 
@@ -663,7 +665,8 @@ def attn_chunk_mma(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, *, se
                    seg_qn: torch.Tensor, seg_ctx: torch.Tensor, block_table: torch.Tensor,
                    items: torch.Tensor, n_items: int, n_heads: int, n_kv_heads: int, head_dim: int,
                    page_tokens: int, window: int, scale: float, n_splits: int = 1,
-                   part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None) -> None:
+                   part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None,
+                   keep_first: int = 0, sink: bool = False) -> None:
     """Attention of portions of prompts on the tensor cores: ``items`` [n_items, 2] =
     (segment, first query of a 64-query tile); otherwise as :func:`attn_chunk`.  ``n_splits`` > 1
     (:func:`attn_chunk_mma_splits`) with scratch of :func:`attn_chunk_mma_scratch` floats: the keys of
@@ -682,7 +685,8 @@ def attn_chunk_mma(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, *, se
     code = _lib("attention_mma").locus_attn_chunk_mma(
         _p(q), _p(pool), _p(out), _p(seg_q0), _p(seg_qn), _p(seg_ctx), _p(block_table), I(block_table.shape[1]),
         _p(items), I(n_items), I(n_heads), I(n_kv_heads), I(head_dim), I(page_tokens), I(window), F(scale),
-        I(n_splits), _p(part_o if n_splits > 1 else None), _p(part_ml if n_splits > 1 else None), _stream()
+        I(n_splits), _p(part_o if n_splits > 1 else None), _p(part_ml if n_splits > 1 else None), I(keep_first),
+        I(1 if sink else 0), _stream()
     )
     if n_splits > 1 and code == 0:
         _count_launches(1)
@@ -817,7 +821,7 @@ def decode_streams(head_dim: int, dtype: torch.dtype, page_tokens: int, max_item
 
 
 def decode_units(max_items: int, n_heads: int, head_dim: int, dtype: torch.dtype, max_splits: int, device,
-                 page_tokens: int = 64, n_kv_heads: int = 0) -> int:
+                 page_tokens: int = 64, n_kv_heads: int = 0, fixed_ranges: bool = False) -> int:
     """How many partial results the scratch of :func:`attn_decode` should hold for batches of up to
     ``max_items`` requests.  The streaming kernels (:func:`decode_streams`, :func:`attn_decode_gqa_takes`) want
     one per (request, head) plus eight rounds of the grid's warps, so that short batches can be cut finely; the
@@ -829,6 +833,8 @@ def decode_units(max_items: int, n_heads: int, head_dim: int, dtype: torch.dtype
     except Exception:  # no GPU (host tests with emulated kernels)
         n_sm = 148
     streaming = max_items * n_heads + 8 * 16 * n_sm
+    if fixed_ranges:   # a window that keeps first tokens: the split kernel
+        return max(streaming, max_items * n_heads * max_splits)
     if decode_streams(head_dim, dtype, page_tokens, max_items):
         return streaming
     if n_kv_heads > 0 and attn_decode_gqa_takes(dtype, n_heads, n_kv_heads, head_dim, page_tokens,
@@ -857,8 +863,11 @@ def attn_decode(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, *, seg_q
                 seg_qn: torch.Tensor, seg_ctx: torch.Tensor, block_table: torch.Tensor,
                 items: torch.Tensor, n_items: int, n_heads: int, n_kv_heads: int, head_dim: int,
                 page_tokens: int, window: int, scale: float, part_o: torch.Tensor,
-                part_ml: torch.Tensor, counters: torch.Tensor, max_splits: int) -> None:
-    """Attention of single new tokens: ``items`` [n_items] = segments with one new token.
+                part_ml: torch.Tensor, counters: torch.Tensor, max_splits: int, keep_first: int = 0,
+                sink: bool = False) -> None:
+    """Attention of single new tokens: ``items`` [n_items] = segments with one new token.  ``keep_first``, ``sink``
+    as for :func:`attn_chunk` (such a step runs on the per-head kernels; with kept tokens on the one whose ranges are
+    fixed, which wants scratch for ``max_splits`` ranges per request and head).
 
     ``part_o`` (float32, units * head_dim) and ``part_ml`` (float32, 2 * units) are scratch for
     partial results, ``units`` as :func:`decode_units` gives it (at least n_items * n_heads);
@@ -877,7 +886,7 @@ def attn_decode(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, *, seg_q
     _need(pool.numel() * pool.element_size() < (64 << 30), "attn_decode: a layer's cache pool of 64 GiB or more")
     _i32(counters, "counters")
     _need(counters.numel() >= n_items * n_heads, "attn_decode: counters too small")
-    if attn_decode_gqa_takes(q.dtype, n_heads, n_kv_heads, head_dim, page_tokens, n_items):
+    if not (keep_first or sink) and attn_decode_gqa_takes(q.dtype, n_heads, n_kv_heads, head_dim, page_tokens, n_items):
         # several query heads per key/value head: the kernel that reads every cache row once for its whole group
         code = _lib("attention_gqa").locus_attn_decode_gqa(
             _p(q), _p(pool), _p(out), _p(seg_q0), _p(seg_ctx), _p(block_table), I(block_table.shape[1]), _p(items),
@@ -891,7 +900,7 @@ def attn_decode(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, *, seg_q
         _p(q), I(dtype_code(q.dtype)), _p(pool), _p(out), _p(seg_q0), _p(seg_qn), _p(seg_ctx),
         _p(block_table), I(block_table.shape[1]), _p(items), I(n_items), I(n_heads), I(n_kv_heads),
         I(head_dim), I(page_tokens), I(window), F(scale), _p(part_o), _p(part_ml), _p(counters), I(max_splits),
-        ctypes.c_longlong(max_units), _stream()
+        ctypes.c_longlong(max_units), I(keep_first if window > 0 else 0), I(1 if sink else 0), _stream()
     )
     _check(code, "attn_decode", f"(heads {n_heads}/{n_kv_heads}, head_dim {head_dim})")
 
@@ -1636,6 +1645,139 @@ def ssm_out(y: torch.Tensor, act: torch.Tensor, proj: torch.Tensor, off_z: int, 
                                              _p(d_skip), I(dtype_code(d_skip.dtype)), _p(w), I(dtype_code(w.dtype)), F(eps),
                                              _p(out), I(dtype_code(out.dtype)), I(T), I(parts), I(inner), I(v_dim), _stream())
     _check(code, "ssm_out")
+
+
+# ---------------------------------------------------------------------------
+# between a stacked projection and its attention or recurrence (csrc/short_conv.cu), the gated delta rule
+# (csrc/delta_rule.cu)
+
+PREP_MAX_TAPS = 16
+PREP_MAX_DIM = 256
+HEAD_NORMS = {None: 0, "rms": 1, "unit": 2}
+
+
+def head_prep(proj: torch.Tensor, *, offsets, heads, dims, laid, state_slots: torch.Tensor, seg_q0: torch.Tensor,
+              seg_qn: torch.Tensor, n_seg: int, longest_new: int, positions: torch.Tensor, q_out: torch.Tensor,
+              k_out: Optional[torch.Tensor] = None, v_out: Optional[torch.Tensor] = None,
+              pool: Optional[torch.Tensor] = None, slots: Optional[torch.Tensor] = None, page_tokens: int = 0,
+              write_kv: bool = True, conv: Optional[torch.Tensor] = None, state: Optional[torch.Tensor] = None,
+              conv_offset: int = 0, move_state: bool = True, act: bool = False,
+              inv_freq: Optional[torch.Tensor] = None, rot: int = 0, norm: Optional[str] = None, eps: float = 0.0,
+              q_scale: float = 1.0, gates=None) -> None:
+    """From the float32 rows ``proj`` of a stacked projection to q in rows and k, v in rows or cache pages, in one
+    launch.  ``offsets``, ``heads``, ``dims``, ``laid``: for q, k, v the first column in ``proj``, the number of heads,
+    the per-head size and the size a head is laid out at in the output (zeros behind its own elements).  In this
+    order, each only if given: ``conv`` [channels, taps] (the channels of q, k, v one behind the other), a causal
+    convolution over time per channel, y_t = sum_j conv[c, j] u_(t - taps + 1 + j), whose inputs before a portion's
+    first token come from the request's slot of ``state`` ([channels, taps - 1] floats from ``conv_offset`` on;
+    moved on by the portion's tokens in the same call unless ``move_state`` is off); ``act``: silu; ``inv_freq``
+    [rot / 2]: q's and k's pairs (i, i + rot / 2) rotated by position * inv_freq[i]; ``norm`` "rms": q and k divided
+    by sqrt(mean(x^2) + eps) per head, "unit": by sqrt(sum(x^2) + eps); ``q_scale`` on q.  The outputs share one
+    element type; with ``pool`` (a layer's pages [n_pages, 2, heads_k, page_tokens, laid]) k and v go to ``slots``.
+    ``gates`` = (beta, decay, off_b, off_a, a_log, dt_bias): also beta = sigmoid(proj[:, off_b + h]) and decay =
+    exp(-exp(a_log[h]) * softplus(proj[:, off_a + h] + dt_bias[h])), [T, heads] float32 each."""
+    _f32c(proj, "head_prep: proj")
+    _cuda_c(q_out, "q_out")
+    _i32(positions, "positions")
+    sizes = (ctypes.c_int * 12)(*[int(v) for v in (*offsets, *heads, *dims, *laid)])
+    out_dt = q_out.dtype
+    _need(q_out.shape[1] == heads[0] * laid[0], "head_prep: q_out width")
+    if pool is not None:
+        _cuda_c(pool, "pool")
+        _i32(slots, "slots")
+        _need(pool.dtype == out_dt and tuple(pool.shape[1:]) == (2, heads[1], page_tokens, laid[1]) and laid[1] == laid[2],
+              "head_prep: pool layout")
+    elif heads[1] or heads[2]:
+        for t, w in ((k_out, 1), (v_out, 2)):
+            _need(t is not None and t.is_cuda and t.is_contiguous() and t.dtype == out_dt and t.shape[1] == heads[w] * laid[w],
+                  "head_prep: k_out, v_out rows")
+    taps = 1
+    state_ptr, stride = None, 0
+    if conv is not None:
+        _cuda_c(conv, "conv")
+        channels = sum(h * d for h, d in zip(heads, dims))
+        taps = conv.shape[1]
+        _need(conv.shape[0] == channels and 1 <= taps <= PREP_MAX_TAPS, "head_prep: conv [channels, taps]")
+        if taps > 1:
+            _need(state is not None and state.is_cuda and state.dtype == torch.float32 and state.dim() == 2
+                  and state.stride(1) == 1 and conv_offset + channels * (taps - 1) <= state.shape[1], "head_prep: state")
+            state_ptr, stride = ctypes.c_void_p(state.data_ptr() + 4 * conv_offset), state.stride(0)
+    if inv_freq is not None:
+        _need(inv_freq.dtype == torch.float32 and inv_freq.is_cuda and inv_freq.numel() == rot // 2, "head_prep: inv_freq [rot / 2]")
+    beta = decay = a_log = dt_bias = None
+    off_b = off_a = gate_heads = gate_dt = 0
+    if gates is not None:
+        beta, decay, off_b, off_a, a_log, dt_bias = gates
+        gate_heads = beta.shape[1]
+        _need(beta.dtype == decay.dtype == torch.float32 and beta.is_contiguous() and decay.is_contiguous()
+              and decay.shape[1] == gate_heads and a_log.numel() == gate_heads and dt_bias.numel() == gate_heads
+              and a_log.dtype == dt_bias.dtype, "head_prep: gates")
+        gate_dt = dtype_code(a_log.dtype)
+    code = _lib("short_conv").locus_head_prep(
+        _p(proj), I(proj.stride(0)), sizes, _p(conv), I(dtype_code(conv.dtype) if conv is not None else 0), I(taps),
+        I(1 if act else 0), state_ptr, LL(stride), I(1 if move_state else 0), _p(state_slots), _p(seg_q0), _p(seg_qn),
+        I(n_seg), I(longest_new), _p(positions), _p(inv_freq), I(rot if inv_freq is not None else 0), I(HEAD_NORMS[norm]),
+        F(eps), F(q_scale), _p(q_out), _p(k_out), _p(v_out), _p(pool), _p(slots), I(page_tokens), I(1 if write_kv else 0),
+        I(dtype_code(out_dt)), _p(beta), _p(decay), I(off_b), I(off_a), I(gate_heads), _p(a_log), _p(dt_bias), I(gate_dt),
+        _stream())
+    if code == 0 and conv is not None and taps > 1 and move_state and n_seg > 0 and longest_new > 0:
+        _count_launches(1)
+    _check(code, "head_prep")
+
+
+def gate_rows(o: torch.Tensor, proj: torch.Tensor, off: int, *, n_heads: int, dim: int, laid: int) -> None:
+    """o[t, h, :dim] *= sigmoid(proj[t, off + h * dim + .]) in place; o's heads are laid out at ``laid`` elements."""
+    _cuda_c(o, "o")
+    _f32c(proj, "gate_rows: proj")
+    _need(o.shape[1] == n_heads * laid and proj.shape[1] >= off + n_heads * dim and proj.shape[0] >= o.shape[0], "gate_rows: shapes")
+    code = _lib("short_conv").locus_gate_rows(_p(o), I(dtype_code(o.dtype)), I(o.stride(0)), _p(proj), I(proj.stride(0)),
+                                              I(off), I(n_heads * dim), I(dim), I(laid), I(o.shape[0]), _stream())
+    _check(code, "gate_rows")
+
+
+DELTA_MAX_DIM = 256
+
+
+def delta_rule(q: torch.Tensor, off_q: int, k: torch.Tensor, off_k: int, v: torch.Tensor, off_v: int, beta: torch.Tensor,
+               decay: torch.Tensor, state: torch.Tensor, state_offset: int, state_slots: torch.Tensor, seg_q0: torch.Tensor,
+               seg_qn: torch.Tensor, n_seg: int, out: torch.Tensor, *, n_heads: int, heads_per_group: int, dim: int,
+               v_dim: int) -> None:
+    """The gated delta rule per request and head over every segment's new tokens in order, from and into the request's
+    state slot: S <- decay S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q.  ``q``, ``k``, ``v``: float32 row matrices
+    in which head h's q and k start at column ``off_q`` / ``off_k`` + (h // heads_per_group) * dim and its v at
+    ``off_v`` + h * v_dim; ``beta``, ``decay`` [T, n_heads] float32; head h's state [dim, v_dim] starts ``state_offset``
+    + h * dim * v_dim floats into a slot of ``state`` [n_slots, floats]; ``out`` [T, n_heads * v_dim] float32."""
+    for t, name in ((q, "q"), (k, "k"), (v, "v"), (beta, "beta"), (decay, "decay"), (out, "out")):
+        _f32c(t, f"delta_rule: {name}")
+    _i32(state_slots, "state_slots")
+    _need(state.is_cuda and state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1
+          and state_offset + n_heads * dim * v_dim <= state.shape[1], "delta_rule: the state does not hold the heads")
+    _need(beta.shape[1] == n_heads and decay.shape[1] == n_heads and beta.is_contiguous() and decay.is_contiguous(),
+          "delta_rule: beta, decay [T, n_heads]")
+    _need(out.shape[1] == n_heads * v_dim and dim <= DELTA_MAX_DIM, "delta_rule: out [T, n_heads * v_dim], dim <= 256")
+    code = _lib("delta_rule").locus_delta_scan(
+        _p(q), I(q.stride(0)), I(off_q), _p(k), I(k.stride(0)), I(off_k), _p(v), I(v.stride(0)), I(off_v), _p(beta),
+        _p(decay), ctypes.c_void_p(state.data_ptr() + 4 * state_offset), LL(state.stride(0)), _p(state_slots), _p(seg_q0),
+        _p(seg_qn), I(n_seg), _p(out), I(out.stride(0)), I(n_heads), I(heads_per_group), I(dim), I(v_dim), _stream())
+    _check(code, "delta_scan", f"(heads {n_heads}, dim {dim}, v_dim {v_dim})")
+
+
+def delta_out(o: torch.Tensor, proj: torch.Tensor, off_g: int, w: torch.Tensor, eps: float, out: torch.Tensor, *,
+              n_heads: int, v_dim: int) -> None:
+    """out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * w * silu(gate[t, h, :]); the gate: the columns of
+    ``proj`` from ``off_g`` on; ``w`` [v_dim] (one weight for every head) or [n_heads * v_dim]."""
+    _f32c(o, "delta_out: o")
+    _f32c(proj, "delta_out: proj")
+    _cuda_c(out, "out")
+    _cuda_c(w, "w")
+    T = out.shape[0]
+    _need(o.is_contiguous() and o.shape[1] == out.shape[1] == n_heads * v_dim and w.numel() in (v_dim, n_heads * v_dim)
+          and proj.shape[1] >= off_g + n_heads * v_dim, "delta_out: shapes")
+    code = _lib("delta_rule").locus_delta_out(_p(o), _p(proj), I(proj.stride(0)), I(off_g), _p(w), I(dtype_code(w.dtype)),
+                                              I(w.numel()), F(eps), _p(out), I(dtype_code(out.dtype)), I(T), I(n_heads),
+                                              I(v_dim), _stream())
+    _check(code, "delta_out")
+
 
 
 def apply_penalties(logits: torch.Tensor, history: torch.Tensor, repeat: torch.Tensor,

@@ -16,6 +16,17 @@ Values may have another size than queries and keys (``v_dim``), and either size 
 kernels take: the heads are then laid out at the next multiple of 16 that holds both, with zero rows in the stacked
 weight and bias and zero columns in the output projection, so that the padding is exact zeros in q, k, v and the cache
 and contributes nothing to a score or an output.  The score's factor is then the caller's (``softmax_scale``).
+
+Further forms, each an option of its own: a window that keeps a request's first ``keep_first`` tokens in sight (query i
+sees key j <= i if i - j < window or j < keep_first; kept tokens stay at their positions); a softmax with a ``sink`` (one
+more term of score 0 and no value in the denominator); a short causal convolution over time on every channel of q, k
+and v directly behind the projection (``conv_taps``; the last taps - 1 projected rows of a request are its state); q
+and k divided by their root mean square per head behind the rotation (``qk_norm``); the heads' outputs multiplied by
+sigmoid(W_g h) in front of the output projection (``out_gate``); a layer without keys and values of its own
+(``has_kv`` off: it reads the cache of the layer call that the run order names).  With any of these (or ``shaped``)
+the projections are one product into float32 rows [q | k | v | gate] at the stored sizes, and one kernel
+(``kernels.head_prep``) convolves, rotates, norms and writes q and the cache pages at the kernels' head size in
+float32 arithmetic, so that padded heads take a rotation there too.
 """
 from __future__ import annotations
 
@@ -25,7 +36,7 @@ from typing import Optional
 import torch
 
 from .. import kernels as K
-from .base import Mixer, PagedKvSpec, PartSpec, StepPlan, TensorSource, make_part, register_mixer
+from .base import Mixer, PagedKvSpec, PartSpec, StateSpec, StepPlan, TensorSource, make_part, register_mixer
 from .position import NoPosition as _NoRotation
 
 CHUNK_TILE = 16  # queries per work item of the CUDA-core chunk kernel
@@ -70,7 +81,8 @@ class AttentionTiles(StepPlan):
 
 # tensor names below an attention's prefix, by role; an architecture with other names passes its own
 NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
-         "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias", "o_bias": "o_proj.bias"}
+         "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias", "o_bias": "o_proj.bias",
+         "q_conv": "q_proj.conv", "k_conv": "k_proj.conv", "v_conv": "v_proj.conv", "gate": "g_proj.weight"}
 
 
 class Attention(Mixer):
@@ -79,11 +91,26 @@ class Attention(Mixer):
     def __init__(self, prefix: str, *, hidden: int, n_heads: int, n_kv_heads: int, head_dim: int,
                  qkv_bias: bool, o_bias: bool = False, window: int = 0,
                  position: PartSpec = PartSpec("none"), softmax_scale: Optional[float] = None,
-                 v_dim: Optional[int] = None, out_scale: float = 1.0, names: Optional[dict] = None) -> None:
+                 v_dim: Optional[int] = None, out_scale: float = 1.0, names: Optional[dict] = None,
+                 keep_first: int = 0, sink: bool = False, conv_taps: int = 0, qk_norm: Optional[str] = None,
+                 qk_norm_eps: float = 0.0, out_gate: bool = False, has_kv: bool = True, shaped: bool = False,
+                 cache_window: Optional[int] = None, cache_keep: Optional[int] = None) -> None:
         """``v_dim``: the values' size per head where it is not ``head_dim``.  ``out_scale``: a factor on the mixer's
         output (a mixer that runs beside another one).  ``names``: tensor names below the prefix where they differ
-        from ``NAMES``."""
+        from ``NAMES``.  ``keep_first``, ``sink``, ``conv_taps``, ``qk_norm`` ("rms"), ``out_gate``, ``has_kv``,
+        ``shaped``: see the head of the file.  ``cache_window`` / ``cache_keep``: what the layer's pages must hold
+        where that is more than its own window and kept tokens (another layer call reads them with a wider mask)."""
         super().__init__(prefix)
+        self.keep_first, self.sink = (int(keep_first) if window else 0), bool(sink)
+        self.conv_taps, self.qk_norm, self.qk_norm_eps = int(conv_taps), qk_norm, float(qk_norm_eps)
+        self.out_gate, self.has_kv = bool(out_gate), bool(has_kv)
+        self.shaped = bool(shaped or self.conv_taps > 0 or qk_norm or out_gate or not has_kv)
+        if self.conv_taps > K.PREP_MAX_TAPS:
+            raise ValueError(f"attention: a convolution over {conv_taps} tokens (at most {K.PREP_MAX_TAPS})")
+        if qk_norm not in (None, "rms", "unit"):
+            raise ValueError(f"attention: qk_norm {qk_norm!r} (known: rms, unit)")
+        self.cache_window = int(window if cache_window is None else cache_window)
+        self.cache_keep = int(self.keep_first if cache_keep is None else cache_keep) if self.cache_window else 0
         if n_heads % n_kv_heads:
             raise ValueError(f"attention: {n_heads} heads are not a multiple of {n_kv_heads} kv heads")
         self.qk_dim, self.v_dim = int(head_dim), int(v_dim if v_dim is not None else head_dim)
@@ -93,7 +120,7 @@ class Attention(Mixer):
         if not (16 <= laid <= 256):
             raise ValueError(f"attention: heads of {self.qk_dim} (values {self.v_dim}) exceed 256 "
                              "(the attention kernels take no larger head)")
-        if self.padded and not isinstance(make_part("position", position, prefix + ".position"), _NoRotation):
+        if self.padded and not self.shaped and not isinstance(make_part("position", position, prefix + ".position"), _NoRotation):
             raise ValueError("attention: heads that are padded to the kernels' sizes take no rotation")
         head_dim = laid
         self.hidden, self.n_heads, self.n_kv_heads, self.head_dim = hidden, n_heads, n_kv_heads, head_dim
@@ -104,6 +131,15 @@ class Attention(Mixer):
         self.position = make_part("position", position, prefix + ".position")
         self.q_dim = n_heads * head_dim
         self.kv_dim = n_kv_heads * head_dim
+        # the shaped form's stacked projection: [q | k | v | gate] at the stored sizes, its width a multiple of 8
+        kv = self.n_kv_heads if self.has_kv else 0
+        self.in_rows = [("q", 0, n_heads * self.qk_dim)]
+        self.in_rows.append(("k", self.in_rows[-1][1] + self.in_rows[-1][2], kv * self.qk_dim))
+        self.in_rows.append(("v", self.in_rows[-1][1] + self.in_rows[-1][2], kv * self.v_dim))
+        self.in_rows.append(("gate", self.in_rows[-1][1] + self.in_rows[-1][2], n_heads * self.v_dim if self.out_gate else 0))
+        self.in_used = self.in_rows[-1][1] + self.in_rows[-1][2]
+        self.in_width = -(-self.in_used // 8) * 8
+        self.channels = self.in_rows[3][1]   # what the convolution covers: q, k, v
 
     def sub_parts(self):
         return [self.position]
@@ -114,6 +150,18 @@ class Attention(Mixer):
         return [("q", self.n_heads * self.qk_dim), ("k", self.n_kv_heads * self.qk_dim), ("v", self.n_kv_heads * self.v_dim)]
 
     def param_shapes(self):
+        if self.shaped:
+            if getattr(self, "_laid_out", False):   # bind has widened the output projection to the kernels' head size
+                return {n: tuple(t.shape) for n, t in self.params.items()}
+            shapes = {"w_in": (self.in_width, self.hidden)}
+            if self.qkv_bias:
+                shapes["b_in"] = (self.in_width,)
+            if self.conv_taps > 0:
+                shapes["conv"] = (self.channels, self.conv_taps)
+            shapes["wo_stored" if self.head_dim != self.v_dim else "wo"] = (self.hidden, self.n_heads * self.v_dim)
+            if self.o_bias:
+                shapes["bo"] = (self.hidden,)
+            return shapes
         if self.padded and "wqkv" not in self.params:
             # loaded as stored, laid out for the kernels in bind
             shapes = {f"w{r}_stored": (n, self.hidden) for r, n in self._stored()}
@@ -132,6 +180,19 @@ class Attention(Mixer):
 
     def sources(self):
         p, nm = self.prefix, self.names
+        if self.shaped:
+            out = [TensorSource(f"{p}.{nm[r]}", (n, self.hidden), "w_in", row0) for r, row0, n in self.in_rows if n]
+            if self.qkv_bias:
+                out += [TensorSource(f"{p}.{nm[r + '_bias']}", (n,), "b_in", row0, "bias")
+                        for r, row0, n in self.in_rows[:3] if n]
+            if self.conv_taps > 0:
+                out += [TensorSource(f"{p}.{nm[r + '_conv']}", (n, self.conv_taps), "conv", row0, "bias")
+                        for r, row0, n in self.in_rows[:3] if n]
+            out.append(TensorSource(f"{p}.{nm['o']}", (self.hidden, self.n_heads * self.v_dim),
+                                    "wo_stored" if self.head_dim != self.v_dim else "wo"))
+            if self.o_bias:
+                out.append(TensorSource(f"{p}.{nm['o_bias']}", (self.hidden,), "bo", 0, "bias"))
+            return out
         if self.padded:
             out = [TensorSource(f"{p}.{nm[r]}", (n, self.hidden), f"w{r}_stored") for r, n in self._stored()]
             if self.qkv_bias:
@@ -152,6 +213,19 @@ class Attention(Mixer):
         if self.out_scale != 1.0:
             self._scale = rt.shared_object(("row_scale", self.out_scale), lambda: torch.full(
                 (rt.max_tokens,), self.out_scale, dtype=torch.float32, device=rt.device))
+        if self.shaped:
+            P = self.params
+            if "wo_stored" in P:
+                # zero columns behind every head of the output projection (the kernels' head size is wider than a value)
+                wo = torch.zeros((self.hidden, self.q_dim), dtype=P["wo_stored"].dtype, device=P["wo_stored"].device)
+                wo.view(self.hidden, self.n_heads, self.head_dim)[:, :, : self.v_dim] = P["wo_stored"].view(self.hidden, self.n_heads, self.v_dim)
+                del P["wo_stored"]
+                P["wo"] = wo
+                self._laid_out = True
+            P["w_in"][self.in_used:].zero_()
+            if "b_in" in P:
+                P["b_in"][self.in_rows[3][1]:].zero_()   # the gate and the padding have no bias
+            return
         if not self.padded or "wqkv" in self.params:
             return
         # the stored heads at the kernels' head size: zero rows behind every head of q, k and v, zero columns behind
@@ -176,16 +250,51 @@ class Attention(Mixer):
             P["bqkv"] = bqkv
 
     def kernel_modules(self, dtype):
-        return ["elementwise", "gemm_simt", "gemv", "attention"] + (["gemm_skinny", "gemm_tc", "attention_mma", "attention_tc", "attention_gqa"] if dtype == torch.bfloat16 else [])
+        special = bool(self.keep_first or self.sink)   # such an attention runs on the kernels that know of both
+        return (["elementwise", "gemm_simt", "gemv", "attention"] + (["short_conv"] if self.shaped else [])
+                + (["gemm_skinny", "gemm_tc", "attention_mma"] if dtype == torch.bfloat16 else [])
+                + (["attention_tc", "attention_gqa"] if dtype == torch.bfloat16 and not special else []))
 
     def cache_needs(self):
-        return PagedKvSpec(self.n_kv_heads, self.head_dim, self.window), None
+        state = None
+        if self.conv_taps > 1:
+            state = StateSpec((self.channels * (self.conv_taps - 1),), torch.float32)
+        return PagedKvSpec(self.n_kv_heads, self.head_dim, self.cache_window, keep_first=self.cache_keep), state
 
     def step_plans(self):
         return [AttentionTiles()]
 
     # -- forward ------------------------------------------------------------
+    def _forward_shaped(self, h, batch, cache, residual, rt, accumulate) -> None:
+        T = batch.T
+        gb = batch.groups[cache.group]
+        proj = rt.rows(f"attention.proj{self.in_width}", self.in_width, torch.float32, T)
+        K.linear(h, self.params["w_in"], proj, bias=self.params.get("b_in"))
+        table = self.position.rotary_table()
+        if table is not None and (table.magnitude != 1.0 or table.interleaved):
+            raise ValueError("attention: the shaped form rotates half-split pairs without a factor on cosine and sine")
+        if self.conv_taps > 1 and not cache.writes:
+            raise ValueError("attention: a layer call that reads another call's cache has no convolution state of its own")
+        q = rt.rows("attention.q", self.q_dim, rt.dtype, T)
+        kv = self.n_kv_heads if self.has_kv else 0
+        D = self.head_dim
+        K.head_prep(proj, offsets=[r[1] for r in self.in_rows[:3]], heads=(self.n_heads, kv, kv),
+                    dims=(self.qk_dim, self.qk_dim, self.v_dim), laid=(D, D, D), state_slots=batch.state_slots,
+                    seg_q0=batch.seg_q0, seg_qn=batch.seg_qn, n_seg=batch.n_seg,
+                    longest_new=max(batch.host_seg_qn) if batch.host_seg_qn else T, positions=batch.positions, q_out=q,
+                    pool=cache.pool if kv else None, slots=gb.slots if kv else None, page_tokens=gb.page_tokens,
+                    write_kv=cache.writes, conv=self.params.get("conv"), state=cache.state if self.conv_taps > 1 else None,
+                    inv_freq=table.inv_freq if table else None, rot=table.rot_dim if table else 0, norm=self.qk_norm,
+                    eps=self.qk_norm_eps)
+        o = rt.rows("attention.o", self.q_dim, rt.dtype, T)
+        self._attend(q, o, batch, cache, gb, rt)
+        if self.out_gate:
+            K.gate_rows(o, proj, self.in_rows[3][1], n_heads=self.n_heads, dim=self.v_dim, laid=D)
+        K.linear(o, self.params["wo"], residual, bias=self.params.get("bo"), accumulate=accumulate, row_scale=self._scale)
+
     def forward(self, h, batch, cache, residual, rt, accumulate=True) -> None:
+        if self.shaped:
+            return self._forward_shaped(h, batch, cache, residual, rt, accumulate)
         T = batch.T
         gb = batch.groups[cache.group]
         qkv = rt.rows("attention.qkv", self.q_dim + 2 * self.kv_dim, rt.dtype, T)
@@ -205,6 +314,14 @@ class Attention(Mixer):
             page_tokens=gb.page_tokens, write_kv=cache.writes,
         )
         o = rt.rows("attention.o", self.q_dim, rt.dtype, T)
+        self._attend(q, o, batch, cache, gb, rt)
+        K.linear(o, self.params["wo"], residual, bias=self.params.get("bo"), accumulate=accumulate, row_scale=self._scale)
+
+    def _attend(self, q, o, batch, cache, gb, rt) -> None:
+        """o = attention of the step's queries ``q`` over the layer's pages, by the kernels that fit the step."""
+        T = batch.T
+        special = bool(self.keep_first or self.sink)
+        extra = dict(keep_first=self.keep_first, sink=self.sink) if special else {}
         common = dict(seg_q0=batch.seg_q0, seg_qn=batch.seg_qn, seg_ctx=batch.seg_ctx,
                       block_table=gb.block_table, n_heads=self.n_heads, n_kv_heads=self.n_kv_heads,
                       head_dim=self.head_dim, page_tokens=gb.page_tokens, window=self.window,
@@ -219,7 +336,7 @@ class Attention(Mixer):
             keys = max_splits * K.DECODE_SPLIT
             if self.window > 0:
                 keys = min(keys, self.window + K.TC_ATTN_QUERY_BLOCK)
-            if K.attn_chunk_tc_takes(q, self.head_dim, gb.page_tokens, T, keys):
+            if not special and K.attn_chunk_tc_takes(q, self.head_dim, gb.page_tokens, T, keys):
                 n_splits = K.attn_chunk_tc_splits(tiles["n_chunk_items64"], self.n_heads, keys)
                 part_o = part_ml = None
                 if n_splits > 1:
@@ -236,14 +353,14 @@ class Attention(Mixer):
                     part_o = rt.buf("attention.chunk_part_o", (n_o,), torch.float32)
                     part_ml = rt.buf("attention.chunk_part_ml", (n_ml,), torch.float32)
                 K.attn_chunk_mma(q, cache.pool, o, items=tiles["chunk_items64"], n_items=tiles["n_chunk_items64"],
-                                 n_splits=n_splits, part_o=part_o, part_ml=part_ml, **common)
+                                 n_splits=n_splits, part_o=part_o, part_ml=part_ml, **extra, **common)
             else:
-                K.attn_chunk(q, cache.pool, o, items=tiles["chunk_items"], n_items=tiles["n_chunk_items"], **common)
+                K.attn_chunk(q, cache.pool, o, items=tiles["chunk_items"], n_items=tiles["n_chunk_items"], **extra, **common)
         if tiles["n_decode_items"]:
             n = tiles["n_decode_items"]
             # scratch sized once, for the longest context that the block table can describe
             units = K.decode_units(rt.max_segments, self.n_heads, self.head_dim, q.dtype, cap_splits, rt.device,
-                                   gb.page_tokens, self.n_kv_heads)
+                                   gb.page_tokens, self.n_kv_heads, fixed_ranges=self.keep_first > 0)
             part_o = rt.buf("attention.part_o", (units * self.head_dim,), torch.float32)
             part_ml = rt.buf("attention.part_ml", (2 * units,), torch.float32)
             counters = rt.shared_object(
@@ -251,8 +368,7 @@ class Attention(Mixer):
                 lambda: torch.zeros(rt.max_segments * self.n_heads, dtype=torch.int32, device=rt.device),
             )
             K.attn_decode(q, cache.pool, o, items=tiles["decode_items"], n_items=n, part_o=part_o,
-                          part_ml=part_ml, counters=counters, max_splits=max_splits, **common)
-        K.linear(o, self.params["wo"], residual, bias=self.params.get("bo"), accumulate=accumulate, row_scale=self._scale)
+                          part_ml=part_ml, counters=counters, max_splits=max_splits, **extra, **common)
 
 
 register_mixer("attention", Attention)

@@ -102,13 +102,15 @@ class PagedKvSpec:
     of the same width unless ``has_v`` is off (a mixer that keeps one row per token: keys only, or a latent),
     and ``extra_width`` further elements per token in a tensor of their own (per-token fields beside the
     rows, as the reference appends them to its cache row, src/locus/model/arch.cpp:539-542).  ``window`` > 0:
-    only the last ``window`` tokens are kept; pages behind the window go back while the request lives."""
+    only the last ``window`` tokens are kept; pages behind the window go back while the request lives, except
+    those that hold the request's first ``keep_first`` tokens, which such a window keeps in sight."""
 
     n_kv_heads: int
     head_dim: int
     window: int = 0
     has_v: bool = True
     extra_width: int = 0
+    keep_first: int = 0
 
     @property
     def planes(self) -> int:

@@ -26,24 +26,34 @@ from .base import (Arrangement, Part, PartSpec, TensorSource, make_part, registe
 class PreNorm(Arrangement):
     def __init__(self, prefix: str, *, hidden: int, norm: PartSpec, mixer: PartSpec,
                  feed_forward: PartSpec, mixer_prefix: str = "self_attn", ff_prefix: str = "mlp",
-                 norm1_name: str = "input_layernorm", norm2_name: str = "post_attention_layernorm") -> None:
+                 norm1_name: str = "input_layernorm", norm2_name: str = "post_attention_layernorm",
+                 plain_norm_names: bool = False) -> None:
+        """``plain_norm_names``: the norms' tensors carry the plain name of the norm (no ".weight" behind it).
+        ``feed_forward`` may be absent (kind "none"): the layer is then its mixer alone and has no second norm."""
         super().__init__(prefix)
         self.hidden = hidden
-        self.norm1 = make_part("norm", norm, f"{prefix}.{norm1_name}")
+
+        def norm_part(name):
+            spec = PartSpec(norm.kind, {**norm.args, "tensor": f"{prefix}.{name}"}) if plain_norm_names else norm
+            return make_part("norm", spec, f"{prefix}.{name}")
+
+        self.norm1 = norm_part(norm1_name)
         self.mixer = make_part("mixer", mixer, f"{prefix}.{mixer_prefix}")
-        self.norm2 = make_part("norm", norm, f"{prefix}.{norm2_name}")
-        self.ff = make_part("feed_forward", feed_forward, f"{prefix}.{ff_prefix}")
+        self.ff = None if feed_forward.kind == "none" else make_part("feed_forward", feed_forward, f"{prefix}.{ff_prefix}")
+        self.norm2 = norm_part(norm2_name) if self.ff is not None else None
 
     takes_pending_add = True
 
     def sub_parts(self):
-        return [self.norm1, self.mixer, self.norm2, self.ff]
+        return [self.norm1, self.mixer] + ([self.norm2, self.ff] if self.ff is not None else [])
 
     def forward(self, x, batch, cache, rt) -> None:
         T = batch.T
         h = rt.rows("block.h", self.hidden, rt.dtype, T)
         self.norm1.forward(x, h, add=rt.take_pending())
         self.mixer.forward(h, batch, cache, x, rt)
+        if self.ff is None:
+            return
         self.norm2.forward(x, h)
         self.ff.forward(h, batch, x, rt)
 
@@ -199,11 +209,13 @@ class StreamedPreNorm(Arrangement):
 
 
 class Embedding(Part):
-    def __init__(self, prefix: str, *, vocab: int, hidden: int, tensor: str = "", copies: int = 1) -> None:
+    def __init__(self, prefix: str, *, vocab: int, hidden: int, tensor: str = "", copies: int = 1,
+                 scale: float = 1.0) -> None:
         """``tensor``: the checkpoint tensor's name where it is not ``<prefix>.weight``.  ``copies`` > 1: a row of the
-        output holds the embedding that many times (a model with several copies of the residual stream)."""
+        output holds the embedding that many times (a model with several copies of the residual stream).  ``scale``:
+        a factor on the embedding, applied in float32."""
         super().__init__(prefix)
-        self.vocab, self.hidden, self.copies = int(vocab), int(hidden), int(copies)
+        self.vocab, self.hidden, self.copies, self.scale = int(vocab), int(hidden), int(copies), float(scale)
         self.tensor = str(tensor or prefix + ".weight")
 
     def param_shapes(self):
@@ -216,8 +228,8 @@ class Embedding(Part):
         return ["elementwise"]
 
     def forward(self, tokens: torch.Tensor, out: torch.Tensor) -> None:
-        if self.copies > 1:
-            K.embed_rows(tokens, self.params["table"], out, copies=self.copies)
+        if self.copies > 1 or self.scale != 1.0:
+            K.embed_rows(tokens, self.params["table"], out, copies=self.copies, scale=self.scale)
         else:
             K.embed_rows(tokens, self.params["table"], out)
 

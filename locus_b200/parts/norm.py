@@ -1,4 +1,5 @@
-"""Norms.  RMSNorm(eps): out = x * rsqrt(mean(x^2) + eps) * w, statistics in float32.
+"""Norms.  RMSNorm(eps): out = x * rsqrt(mean(x^2) + eps) * w, statistics in float32; with ``offset`` the stored
+weight is taken as w + offset (a weight stored around zero: offset 1).
 LayerNorm(eps): out = (x - mean) / sqrt(var + eps) * w + b (below).
 
 Formula and multiplication order of the reference's ``rmsnorm``
@@ -16,12 +17,19 @@ from .base import Norm, TensorSource, register_norm
 
 
 class RMSNorm(Norm):
-    def __init__(self, prefix: str, *, width: int, eps: float, tensor: str = "") -> None:
-        """``tensor``: the checkpoint tensor's name where it is not ``<prefix>.weight``."""
+    def __init__(self, prefix: str, *, width: int, eps: float, tensor: str = "", offset: float = 0.0) -> None:
+        """``tensor``: the checkpoint tensor's name where it is not ``<prefix>.weight``.  ``offset``: added to the
+        stored weight, in float32 (at bind, so that 1 + w is not rounded to the weight's 16 bits)."""
         super().__init__(prefix)
         self.width = int(width)
         self.eps = float(eps)
+        self.offset = float(offset)
         self.tensor = str(tensor or prefix + ".weight")
+
+    def bind(self, rt) -> None:
+        if self.offset != 0.0 and not getattr(self, "_offset_done", False):
+            self.params["weight"] = (self.params["weight"].float() + self.offset).contiguous()
+            self._offset_done = True
 
     def param_shapes(self):
         return {"weight": (self.width,)}

@@ -20,8 +20,8 @@ def _f(t: torch.Tensor) -> torch.Tensor:
     return t.to(torch.float64 if PRECISE else torch.float32)
 
 
-def embed_rows(tokens, table, out, copies=1):
-    out.copy_(table[tokens.long()].to(out.dtype).repeat(1, copies))
+def embed_rows(tokens, table, out, copies=1, scale=1.0):
+    out.copy_((_f(table[tokens.long()]) * scale).to(out.dtype).repeat(1, copies))
 
 
 def attn_chunk_tc_takes(q, head_dim, page_tokens, n_tokens, max_ctx=0):
@@ -115,36 +115,39 @@ def rope_kv_write(qkv, positions, inv_freq, q_out, pool, slots, *, n_heads, n_kv
         pool[page, 1, :, off, :] = x[t, n_heads + n_kv_heads :].to(pool.dtype)
 
 
-def _attend_one(q, pool, table, p, kvh, page_tokens, window, scale):
+def _attend_one(q, pool, table, p, kvh, page_tokens, window, scale, keep_first=0, sink=False):
     lo = max(0, p - window + 1) if window > 0 else 0
-    ts = list(range(lo, p + 1))
+    ts = list(range(0, min(keep_first, lo))) + list(range(lo, p + 1))
     pages = [int(table[t // page_tokens]) for t in ts]
     assert all(pg >= 0 for pg in pages), "attention reads a page that was given back"
     k = torch.stack([_f(pool[pg, 0, kvh, t % page_tokens]) for pg, t in zip(pages, ts)])
     v = torch.stack([_f(pool[pg, 1, kvh, t % page_tokens]) for pg, t in zip(pages, ts)])
     s = (k @ _f(q)) * scale
+    if sink:
+        s = torch.cat([s, s.new_zeros(1)])
+        return torch.softmax(s, dim=0)[:-1] @ v
     a = torch.softmax(s, dim=0)
     return a @ v
 
 
 def _attn(q, pool, out, seg_list, *, seg_q0, seg_qn, seg_ctx, block_table, n_heads, n_kv_heads, head_dim,
-          page_tokens, window, scale):
+          page_tokens, window, scale, keep_first=0, sink=False):
     group = n_heads // n_kv_heads
     for seg in seg_list:
         q0, qn, ctx = int(seg_q0[seg]), int(seg_qn[seg]), int(seg_ctx[seg])
         for i in range(qn):
             for h in range(n_heads):
                 qv = q[q0 + i].view(n_heads, head_dim)[h]
-                o = _attend_one(qv, pool, block_table[seg], ctx + i, h // group, page_tokens, window, scale)
+                o = _attend_one(qv, pool, block_table[seg], ctx + i, h // group, page_tokens, window, scale, keep_first, sink)
                 out[q0 + i].view(n_heads, head_dim)[h] = o.to(out.dtype)
 
 
 def attn_chunk(q, pool, out, *, seg_q0, seg_qn, seg_ctx, block_table, items, n_items, n_heads, n_kv_heads,
-               head_dim, page_tokens, window, scale):
+               head_dim, page_tokens, window, scale, keep_first=0, sink=False):
     segs = sorted({int(items[i, 0]) for i in range(n_items)})
     _attn(q, pool, out, segs, seg_q0=seg_q0, seg_qn=seg_qn, seg_ctx=seg_ctx, block_table=block_table,
           n_heads=n_heads, n_kv_heads=n_kv_heads, head_dim=head_dim, page_tokens=page_tokens, window=window,
-          scale=scale)
+          scale=scale, keep_first=keep_first, sink=sink)
 
 
 def attn_chunk_mma_splits(n_items, n_heads, max_ctx):
@@ -152,20 +155,20 @@ def attn_chunk_mma_splits(n_items, n_heads, max_ctx):
 
 
 def attn_chunk_mma(q, pool, out, *, seg_q0, seg_qn, seg_ctx, block_table, items, n_items, n_heads, n_kv_heads,
-                   head_dim, page_tokens, window, scale, n_splits=1, part_o=None, part_ml=None):
+                   head_dim, page_tokens, window, scale, n_splits=1, part_o=None, part_ml=None, keep_first=0, sink=False):
     attn_chunk(q, pool, out, seg_q0=seg_q0, seg_qn=seg_qn, seg_ctx=seg_ctx, block_table=block_table, items=items,
                n_items=n_items, n_heads=n_heads, n_kv_heads=n_kv_heads, head_dim=head_dim, page_tokens=page_tokens,
-               window=window, scale=scale)
+               window=window, scale=scale, keep_first=keep_first, sink=sink)
 
 
 def attn_decode(q, pool, out, *, seg_q0, seg_qn, seg_ctx, block_table, items, n_items, n_heads, n_kv_heads,
-                head_dim, page_tokens, window, scale, part_o, part_ml, counters, max_splits):
+                head_dim, page_tokens, window, scale, part_o, part_ml, counters, max_splits, keep_first=0, sink=False):
     segs = [int(items[i]) for i in range(n_items)]
     for s in segs:
         assert int(seg_ctx[s]) // K.DECODE_SPLIT + 1 <= max_splits
     _attn(q, pool, out, segs, seg_q0=seg_q0, seg_qn=seg_qn, seg_ctx=seg_ctx, block_table=block_table,
           n_heads=n_heads, n_kv_heads=n_kv_heads, head_dim=head_dim, page_tokens=page_tokens, window=window,
-          scale=scale)
+          scale=scale, keep_first=keep_first, sink=sink)
 
 
 def _select(logits_row, top_k, renorm, scale, score_fn, sel_bias, n_group, n_group_used, group_score="top2"):
@@ -533,6 +536,107 @@ def mlstm_out(o_raw, m_t, proj, off_g, w, eps, out, *, n_heads, v_dim):
     out[:T] = (u.reshape(T, H * dv) * _f(w) * torch.sigmoid(g)).to(out.dtype)
 
 
+def head_prep(proj, *, offsets, heads, dims, laid, state_slots, seg_q0, seg_qn, n_seg, longest_new, positions, q_out,
+              k_out=None, v_out=None, pool=None, slots=None, page_tokens=0, write_kv=True, conv=None, state=None,
+              conv_offset=0, move_state=True, act=False, inv_freq=None, rot=0, norm=None, eps=0.0, q_scale=1.0, gates=None):
+    widths = [h * d for h, d in zip(heads, dims)]
+    C = sum(widths)
+    taps = conv.shape[1] if conv is not None else 1
+    for seg in range(n_seg):
+        q0, qn, slot = int(seg_q0[seg]), int(seg_qn[seg]), int(state_slots[seg])
+        if qn == 0:
+            continue
+        rows = slice(q0, q0 + qn)
+        xin = torch.cat([_f(proj[rows, o:o + w]) for o, w in zip(offsets, widths)], 1)        # [qn, C]
+        if conv is not None:
+            if taps > 1:
+                old = _f(state[slot, conv_offset:conv_offset + C * (taps - 1)]).view(C, taps - 1)
+                full = torch.cat([old.T, xin], 0)
+            else:
+                full = xin
+            y = torch.zeros_like(xin)
+            for j in range(taps):
+                y = y + full[j:j + qn] * _f(conv)[:, j]
+            if taps > 1 and move_state:
+                state[slot, conv_offset:conv_offset + C * (taps - 1)] = full[qn:].T.reshape(-1).to(state.dtype)
+        else:
+            y = xin
+        if act:
+            y = y / (1.0 + torch.exp(-y))
+        at = 0
+        for which in range(3):
+            H, d, L = heads[which], dims[which], laid[which]
+            x = y[:, at:at + H * d].reshape(qn, H, d).clone()
+            at += H * d
+            if H == 0 or (which > 0 and not write_kv):
+                continue
+            if which < 2 and inv_freq is not None and rot > 0:
+                ang = positions[rows].to(torch.float32)[:, None] * inv_freq[None, :].to(torch.float32)
+                c, s = _f(torch.cos(ang))[:, None, :], _f(torch.sin(ang))[:, None, :]
+                half = rot // 2
+                u, v = x[..., :half].clone(), x[..., half:rot].clone()
+                x[..., :half] = u * c - v * s
+                x[..., half:rot] = v * c + u * s
+            if which < 2 and norm == "rms":
+                x = x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps)
+            elif which < 2 and norm == "unit":
+                x = x / torch.sqrt((x * x).sum(-1, keepdim=True) + eps)
+            if which == 0:
+                x = x * q_scale
+            padded = x.new_zeros(qn, H, L)
+            padded[..., :d] = x
+            if which == 0:
+                q_out[rows] = padded.reshape(qn, H * L).to(q_out.dtype)
+            elif pool is not None:
+                for i in range(qn):
+                    page, off = int(slots[q0 + i]) // page_tokens, int(slots[q0 + i]) % page_tokens
+                    pool[page, which - 1, :, off, :] = padded[i].to(pool.dtype)
+            else:
+                (k_out if which == 1 else v_out)[rows] = padded.reshape(qn, H * L).to(q_out.dtype)
+        if gates is not None:
+            beta, decay, off_b, off_a, a_log, dt_bias = gates
+            G = beta.shape[1]
+            beta[rows] = torch.sigmoid(_f(proj[rows, off_b:off_b + G])).to(beta.dtype)
+            dt = torch.nn.functional.softplus(_f(proj[rows, off_a:off_a + G]) + _f(dt_bias))
+            decay[rows] = torch.exp(-torch.exp(_f(a_log)) * dt).to(decay.dtype)
+
+
+def gate_rows(o, proj, off, *, n_heads, dim, laid):
+    T = o.shape[0]
+    g = torch.sigmoid(_f(proj[:T, off:off + n_heads * dim])).view(T, n_heads, dim)
+    ov = o.view(T, n_heads, laid)
+    ov[..., :dim] = (_f(ov[..., :dim]) * g).to(o.dtype)
+
+
+def delta_rule(q, off_q, k, off_k, v, off_v, beta, decay, state, state_offset, state_slots, seg_q0, seg_qn, n_seg, out, *,
+               n_heads, heads_per_group, dim, v_dim):
+    H, d, dv = n_heads, dim, v_dim
+    for seg in range(n_seg):
+        q0, qn, slot = int(seg_q0[seg]), int(seg_qn[seg]), int(state_slots[seg])
+        S = _f(state[slot, state_offset:state_offset + H * d * dv]).view(H, d, dv).clone()
+        for i in range(qn):
+            r = q0 + i
+            for h in range(H):
+                g = h // heads_per_group
+                qv = _f(q[r, off_q + g * d: off_q + (g + 1) * d])
+                kv = _f(k[r, off_k + g * d: off_k + (g + 1) * d])
+                vv = _f(v[r, off_v + h * dv: off_v + (h + 1) * dv])
+                S[h] = S[h] * _f(decay[r, h])
+                u = _f(beta[r, h]) * (vv - S[h].T @ kv)
+                S[h] = S[h] + kv[:, None] * u[None, :]
+                out[r, h * dv:(h + 1) * dv] = (S[h].T @ qv).to(out.dtype)
+        state[slot, state_offset:state_offset + H * d * dv] = S.reshape(-1).to(state.dtype)
+
+
+def delta_out(o, proj, off_g, w, eps, out, *, n_heads, v_dim):
+    T = out.shape[0]
+    x = _f(o[:T]).view(T, n_heads, v_dim)
+    x = x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps)
+    wv = _f(w).view(-1, v_dim)     # [1, v_dim] (shared) or [heads, v_dim]
+    z = _f(proj[:T, off_g:off_g + n_heads * v_dim]).view(T, n_heads, v_dim)
+    out[:T] = (x * wv * (z / (1.0 + torch.exp(-z)))).reshape(T, -1).to(out.dtype)
+
+
 def ssm_conv(proj, off_xbc, off_dt, conv_w, conv_b, dt_bias, a_log, state, conv_offset, state_slots, seg_q0, seg_qn, n_seg,
              act, keep, take, *, n_heads, longest_new=0):
     C, taps = conv_w.shape
@@ -569,7 +673,7 @@ _NAMES = ["embed_rows", "rmsnorm", "rmsnorm_adds", "attn_chunk_tc_takes", "linea
           "moe_sort", "route_small", "route_small_takes", "route_fused_small", "moe_combine", "gather_rows", "apply_penalties", "sample",
           "cast_rows", "rmsnorm_add", "latent_prep", "latent_q_split", "latent_attn", "heads_to_rows", "retention_scan",
           "retention_gate_norm", "head_tile", "latent_attn_mma_takes", "layernorm", "stream_update", "moe_identity",
-          "gated_recurrence", "mlstm_gates", "mlstm_out", "ssm_conv", "ssm_out"]
+          "gated_recurrence", "mlstm_gates", "mlstm_out", "ssm_conv", "ssm_out", "head_prep", "gate_rows", "delta_rule", "delta_out"]
 
 
 def install(monkeypatch) -> None:
