@@ -99,7 +99,9 @@ def sharpen(name, w):
         elif n.endswith((".left.q", ".left.k")):
             w[n] = t * 3.0                                                   # (their heads are normed: the scale decides)
         elif n.endswith((".mix.q", ".mix.k")):
-            w[n] = t * 9.0
+            w[n] = t * 6.0                                                   # scores around zero: the sink has its say
+        elif n.endswith((".mix.v", ".mix.o")):
+            w[n] = t * 4.0
         elif n.endswith((".q.b", ".k.b", ".v.b", ".o.b")):
             w[n] = t * 10.0
         elif n.endswith((".right.q", ".right.k", ".right.v")):

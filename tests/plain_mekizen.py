@@ -175,7 +175,7 @@ def attention_kv(weights, p: str, m: dict, h: torch.Tensor):
     return k, v
 
 
-def gated_attention(weights, p: str, m: dict, h: torch.Tensor, kv) -> torch.Tensor:
+def gated_attention(weights, p: str, m: dict, h: torch.Tensor, kv, sink: bool = True) -> torch.Tensor:
     """``kv``: (keys, values) of this layer or of the layer it takes them from."""
     H, d, dv = m["heads"], m["dim"], m["vdim"]
     T = h.shape[0]
@@ -185,7 +185,7 @@ def gated_attention(weights, p: str, m: dict, h: torch.Tensor, kv) -> torch.Tens
         q = rotate(q, float(rot["base"]), int(rot["dims"]))
     mask = m.get("mask") or {}
     o = softmax_attention(q, kv[0], kv[1], float(m["scale"]), int(mask.get("size", 0)), int(mask.get("keep_first", 0)),
-                          sink=True)
+                          sink=sink)
     o = o.reshape(T, H * dv) * sigmoid(h @ _w(weights, p + ".g").T)
     return o @ _w(weights, p + ".o").T + _w(weights, p + ".o.b")
 
@@ -199,10 +199,14 @@ def dense_ff(weights, p: str, h: torch.Tensor) -> torch.Tensor:
 # the model
 
 
-def forward(weights: Dict[str, torch.Tensor], cfg: dict, tokens: List[int], layers_out: Optional[list] = None) -> torch.Tensor:
-    """Logits [T, vocab] of one sequence; ``layers_out`` collects the residual stream after every layer."""
+def forward(weights: Dict[str, torch.Tensor], cfg: dict, tokens: List[int], layers_out: Optional[list] = None,
+            sink: bool = True, own_kv: Optional[dict] = None) -> torch.Tensor:
+    """Logits [T, vocab] of one sequence; ``layers_out`` collects the residual stream after every layer.  For tests that
+    show that a fault would be seen: ``sink`` off leaves the one out of the softmax's denominator; ``own_kv`` {layer:
+    other layer} lets a layer project keys and values from its own input with the other layer's weights instead of
+    using that layer's."""
     eps = float(cfg["norm"]["eps"])
-    x = _w(weights, "embed")[torch.tensor(tokens)] * float(cfg["embedding"]["scale"])
+    x = _w(weights, "embed")[torch.tensor(tokens)] * float((cfg.get("embedding") or {}).get("scale", 1.0))
     kvs = {}
     for i, layer in enumerate(cfg["layers"]):
         p, m = f"l{i}", layer["mixer"]
@@ -214,7 +218,10 @@ def forward(weights: Dict[str, torch.Tensor], cfg: dict, tokens: List[int], laye
             if src is None:
                 kvs[i] = attention_kv(weights, p + ".mix", m, h)
                 src = i
-            x = x + gated_attention(weights, p + ".mix", m, h, kvs[src])
+            kv = kvs[src]
+            if own_kv and i in own_kv:
+                kv = attention_kv(weights, f"l{own_kv[i]}.mix", m, h)
+            x = x + gated_attention(weights, p + ".mix", m, h, kv, sink)
         else:
             raise ValueError(layer["type"])
         if layer.get("mlp") is not None:
