@@ -1,7 +1,9 @@
-"""Prefill and decode throughput of the Lalepel or the Pozozen design at layer sizes that resemble a real model's,
-beside the Qwen2-MoE architecture at equal sizes (random weights, synthetic token ids, one GPU).
+"""Prefill and decode throughput of the Lalepel, the Pozozen or the Mekizen design at layer sizes that resemble a real
+model's, beside the closest architecture at equal sizes (random weights, synthetic token ids, one GPU): Qwen2-MoE for
+Lalepel and Pozozen; for Mekizen both Pozozen (the closest mixers: windowed attention beside a float32 recurrence) and
+Qwen2-MoE.
 
-    python -m locus_b200.tools.arch_bench [--design lalepel|pozozen] [--size m|s] [--layers 4] [--prefill 2048]
+    python -m locus_b200.tools.arch_bench [--design lalepel|pozozen|mekizen] [--size m|s] [--layers 4] [--prefill 2048]
                                           [--batch 8] [--context 4096] [--steps 16] [--warmup 3] [--dtype bf16|fp32]
                                           [--kernels]
 
@@ -9,7 +11,9 @@ Both models get the same width, head count and head sizes, experts, picks per to
 vocabulary; Lalepel's layers cycle through (latent attention, latent attention, retention, latent attention), all
 with routed experts; Pozozen's through (attention beside a state-space mixer, matrix memory, matrix memory, attention
 beside a state-space mixer) over two copies of the residual stream, with four identity experts beside the routed ones
-in eight (or four) groups of which half stay open.  Timed on the device with CUDA events after warm-up; every step reads its weights (several
+in eight (or four) groups of which half stay open; Mekizen's through (convolved attention beside a gated delta rule,
+windowed attention with kept first tokens and a sink, the same beside a delta rule again, attention on the second
+layer's keys and values), all with a dense squared-ReLU feed-forward of four times the width.  Timed on the device with CUDA events after warm-up; every step reads its weights (several
 hundred MB: more than the L2 holds).  ``--kernels`` adds, for one eager prefill step and one eager decode step of
 each model, the time by kernel entry point, and for the mixers' own kernels what their bytes or flops would take
 at the measured peaks.  Prints one JSON line.
@@ -61,6 +65,28 @@ def pozozen_config(z, n_layers):
             "streams": 2, "layers": [(mem if i % 4 in (1, 2) else par) for i in range(n_layers)]}
 
 
+def mekizen_config(z, n_layers):
+    rot = {"base": 10000.0, "dims": z["dim"]}
+    mlp = {"kind": "dense", "ff": 4 * z["width"]}
+
+    def attn(kv_from=None):
+        m = {"heads": z["heads"], "kv_heads": z["heads"], "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5,
+             "rot": rot, "mask": {"size": z["window"], "keep_first": 4}}
+        if kv_from is not None:
+            m["kv_from"] = kv_from
+        return {"type": "attention", "mlp": mlp, "mixer": m}
+
+    par = {"type": "parallel", "mlp": mlp, "mixer": {
+        "left": {"heads": z["heads"], "kv_heads": z["heads"], "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5,
+                 "rot": rot, "conv": 4},
+        "right": {"heads": z["heads"], "kv_heads": z["heads"], "dim": z["ret_dim"], "vdim": z["vdim"], "conv": 4}}}
+    layers = []
+    for i in range(n_layers):
+        layers.append(par if i % 2 == 0 else attn(i - 2 if i % 4 == 3 else None))
+    return {"architecture": "Mekizen", "width": z["width"], "vocab": z["vocab"], "norm": {"eps": 1e-6},
+            "embedding": {"scale": 1.0}, "layers": layers}
+
+
 def qwen_config(z, n_layers, max_pos):
     hd = z["dim"] + z["rot"] if (z["dim"] + z["rot"]) in (64, 128) else z["dim"]
     return {"architectures": ["Qwen2MoeForCausalLM"], "model_type": "qwen2_moe", "num_hidden_layers": n_layers,
@@ -103,8 +129,11 @@ def run(args) -> dict:
     pk = peaks()
     gen = torch.Generator().manual_seed(5)
     design = args.design
-    own = lalepel_config(z, args.layers) if design == "lalepel" else pozozen_config(z, args.layers)
-    raws = {design: own, "qwen2_moe": qwen_config(z, args.layers, max(ctx, T) + 8)}
+    own = {"lalepel": lalepel_config, "pozozen": pozozen_config, "mekizen": mekizen_config}[design](z, args.layers)
+    raws = {design: own}
+    if design == "mekizen":
+        raws["pozozen"] = pozozen_config(z, args.layers)
+    raws["qwen2_moe"] = qwen_config(z, args.layers, max(ctx, T) + 8)
     raws["qwen2_moe"].pop("_head")
     out = {}
     for name, raw in raws.items():
@@ -186,6 +215,28 @@ def run(args) -> dict:
     H, R = z["heads"], z["kv_rank"] + z["rot"]
     keys_avg = sum(min(p + 1, z["window"]) for p in range(T)) / T
     fma_tflops = 148 * 128 * 2 * 1.965e9 / 1e12       # float32 FMAs of the CUDA cores at the top clock
+    if design == "mekizen":
+        d, dv = z["ret_dim"], z["vdim"]
+        chan = 2 * H * d + H * dv
+        bounds = {
+            # the left side sees every earlier token; a windowed layer the window and the kept tokens
+            "attn_full_prefill_us": 2.0 * T * (T + 1) / 2 * H * 2 * z["dim"] / (pk["bf16_tflops"] * 1e12) * 1e6,
+            "attn_window_prefill_us": 2.0 * T * keys_avg * H * 2 * z["dim"] / (pk["bf16_tflops"] * 1e12) * 1e6,
+            "attn_full_decode_us": B * ctx * 2 * H * z["dim"] * el / (pk["hbm_gbs"] * 1e9) * 1e6,
+            "attn_window_decode_us": B * min(ctx, z["window"] + 4) * 2 * H * z["dim"] * el / (pk["hbm_gbs"] * 1e9) * 1e6,
+            # per token and head S^T k, S^T q and the decayed rank-one update, float32 FMAs
+            "delta_prefill_us": 2.0 * T * H * 3 * d * dv / (fma_tflops * 1e12) * 1e6,
+            "delta_decode_us": B * H * d * dv * 4 * 2 / (pk["hbm_gbs"] * 1e9) * 1e6,
+            # float32 rows in, float32 rows (the delta rule's side) or 16-bit rows and pages (the attention side) out
+            "head_prep_delta_prefill_us": T * (chan + 2 * H) * 4 * 2 / (pk["hbm_gbs"] * 1e9) * 1e6,
+            "head_prep_attn_prefill_us": T * 3 * H * z["dim"] * (4 + el) / (pk["hbm_gbs"] * 1e9) * 1e6,
+            "fp32_fma_tflops": fma_tflops,
+        }
+        return {"metric": f"prefill and decode tokens/s, Mekizen beside Pozozen and Qwen2-MoE at equal layer sizes "
+                          f"({args.size}, {args.layers} layers, {args.dtype})",
+                "size": z, "layers": args.layers, "dtype": args.dtype, "data": "synthetic", "designs": out,
+                "bounds_per_layer": bounds, "peaks": pk,
+                "l2": "no flush: every step reads its weights, more than the 126 MB L2"}
     if design == "pozozen":
         sh, sdv, sn = 2 * z["width"] // z["ssm_vdim"], z["ssm_vdim"], z["ssm_state"]
 
@@ -227,7 +278,7 @@ def run(args) -> dict:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="arch_bench", description=__doc__.split("\n\n")[0])
-    ap.add_argument("--design", default="lalepel", choices=["lalepel", "pozozen"])
+    ap.add_argument("--design", default="lalepel", choices=["lalepel", "pozozen", "mekizen"])
     ap.add_argument("--size", default="m", choices=sorted(SIZES))
     ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--prefill", type=int, default=2048)

@@ -5,7 +5,8 @@
     python -m locus_b200.tools.kernel_bench attn_chunk --tokens 2048 --ctx 0
     python -m locus_b200.tools.kernel_bench experts --tokens 2048 [--experts 60 --top-k 4 --k 2048 --n 1408] [--part up|down]
     python -m locus_b200.tools.kernel_bench recurrence --tokens 2048 --batch 1 [--heads 16 --head-dim 128 --v-dim 128]
-                                                       [--per-group 1] [--ones] [--retention]
+                                                       [--per-group 1] [--ones] [--retention | --delta]
+    python -m locus_b200.tools.kernel_bench head_prep --tokens 2048 --batch 1 [--window 4096]
 
 Times with CUDA events after warm-up.  Weights rotate through enough copies that the L2
 cannot hold them (``linear``); attention reads a cache larger than the L2 at the default
@@ -208,6 +209,8 @@ def bench_recurrence(args) -> None:
     q0 = torch.arange(0, T, n, dtype=torch.int32, device=dev)
     qn = torch.full((B,), n, dtype=torch.int32, device=dev)
     slots = torch.arange(B, dtype=torch.int32, device=dev)
+    if args.delta:
+        return _bench_delta(args, B, n, H, d, dv, G, q0, qn, slots, g)
     if args.retention:
         rows = (torch.randn(T, 2 * H * d + 2 * H * dv, generator=g) * 0.3).to(dev)
         state = torch.zeros(B, H, d, dv, device=dev)
@@ -236,6 +239,74 @@ def bench_recurrence(args) -> None:
           f"{fl / us / 1e6:.2f} TFLOP/s (float32 FMA), {by / us / 1e3:.0f} GB/s")
 
 
+def _bench_delta(args, B, n, H, d, dv, G, q0, qn, slots, g) -> None:
+    """The gated delta rule at the same sizes: unit keys, steps in (0, 1), decays near 1.  FLOPs: S^T k, S^T q and the
+    decayed rank-one update per token and head; bytes: the states read and written, the operands, the outputs."""
+    dev, T, Gn = "cuda:0", B * n, H // G
+    q = (torch.randn(T, Gn * d, generator=g) * d ** -0.5).to(dev)
+    k = torch.nn.functional.normalize(torch.randn(T, Gn, d, generator=g), dim=-1).reshape(T, Gn * d).to(dev)
+    v = (torch.randn(T, H * dv, generator=g) * 0.3).to(dev)
+    beta = torch.rand(T, H, generator=g).to(dev)
+    decay = (torch.rand(T, H, generator=g) * 0.1 + 0.9).to(dev)
+    state = torch.zeros(B, H * d * dv, device=dev)
+    out = torch.zeros(T, H * dv, device=dev)
+
+    def fn():
+        K.delta_rule(q, 0, k, 0, v, 0, beta, decay, state, 0, slots, q0, qn, B, out, n_heads=H, heads_per_group=G, dim=d,
+                     v_dim=dv)
+    us = _time(fn, args.iters, args.graph)
+    by = 4.0 * (2 * B * H * d * dv + q.numel() + k.numel() + v.numel() + out.numel())
+    fl = 2.0 * T * H * 3 * d * dv
+    print(f"gated delta rule: {B} x {n} tokens, {H} heads of {d} x {dv}: {us:.1f} us/call, "
+          f"{fl / us / 1e6:.2f} TFLOP/s (float32 FMA), {by / us / 1e3:.0f} GB/s")
+
+
+def bench_head_prep(args) -> None:
+    """What stands between a stacked projection and its attention or recurrence, on ``--batch`` requests of ``--tokens``
+    new tokens: the short convolution from and into the slot, silu, unit norms and the gates (the delta rule's side), or
+    with ``--window`` > 0 the convolution, the rotation, the head norms and the write into pages (the attention side).
+    Bytes: the float32 rows read, the outputs written."""
+    dev = "cuda:0"
+    B, n, H, Hk, d, dv, taps = args.batch, args.tokens, args.heads, args.kv_heads, args.head_dim, args.v_dim, 4
+    T = B * n
+    g = torch.Generator().manual_seed(1)
+    paged = args.window > 0
+    heads, dims = ((H, Hk, Hk), (d, d, d)) if paged else ((Hk, Hk, H), (d, d, dv))
+    widths = [h * x for h, x in zip(heads, dims)]
+    C = sum(widths)
+    gh = 0 if paged else H
+    proj = (torch.randn(T, C + 2 * gh, generator=g) * 0.5).to(dev)
+    conv = (torch.randn(C, taps, generator=g) * 0.5).to(dev).to(torch.bfloat16)
+    state = torch.zeros(B, C * (taps - 1), device=dev)
+    q0 = torch.arange(0, T, n, dtype=torch.int32, device=dev)
+    qn = torch.full((B,), n, dtype=torch.int32, device=dev)
+    slots = torch.arange(B, dtype=torch.int32, device=dev)
+    pos = torch.arange(n, dtype=torch.int32).repeat(B).to(dev)
+    odt = torch.bfloat16 if paged and args.dtype == "bfloat16" else torch.float32
+    qo = torch.zeros(T, widths[0], dtype=odt, device=dev)
+    offs = (0, widths[0], widths[0] + widths[1])
+    if paged:
+        P = args.page_tokens
+        pool = torch.zeros(-(-T // P), 2, Hk, P, d, dtype=odt, device=dev)
+        where = torch.arange(T, dtype=torch.int32, device=dev)
+        inv = (1e4 ** (-torch.arange(0, d, 2, dtype=torch.float32) / d)).to(dev)
+        kw = dict(q_out=qo, pool=pool, slots=where, page_tokens=P, inv_freq=inv, rot=d, norm="rms", eps=1e-6)
+    else:
+        ko, vo = torch.zeros(T, widths[1], device=dev), torch.zeros(T, widths[2], device=dev)
+        beta, decay = torch.zeros(T, H, device=dev), torch.zeros(T, H, device=dev)
+        a_log, dtb = torch.zeros(H, device=dev), torch.zeros(H, device=dev)
+        kw = dict(q_out=qo, k_out=ko, v_out=vo, act=True, norm="unit", eps=1e-6, q_scale=d ** -0.5,
+                  gates=(beta, decay, C, C + H, a_log, dtb))
+
+    def fn():
+        K.head_prep(proj, offsets=offs, heads=heads, dims=dims, laid=dims, state_slots=slots, seg_q0=q0, seg_qn=qn, n_seg=B,
+                    longest_new=n, positions=pos, conv=conv, state=state, conv_offset=0, **kw)
+    us = _time(fn, args.iters, args.graph)
+    by = 4.0 * proj.numel() + qo.numel() * qo.element_size() + (2 * T * Hk * d * qo.element_size() if paged else 4.0 * (widths[1] + widths[2] + 2 * H) * T)
+    print(f"head_prep ({'attention side' if paged else 'delta side'}): {B} x {n} tokens, {C} channels, {taps} taps: "
+          f"{us:.1f} us/call, {by / us / 1e3:.0f} GB/s")
+
+
 def bench_sample(args) -> None:
     """The sampling kernel on --rows rows of --vocab random float32 logits: greedy, temperature 0.8 alone, with
     top-k 50, with top-p 0.9, with top-k 50 + top-p 0.9 + min-p 0.05.  --one-block keeps every row on the one-block
@@ -258,7 +329,7 @@ def bench_sample(args) -> None:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="kernel_bench")
-    ap.add_argument("kernel", choices=["linear", "attn_decode", "attn_chunk", "experts", "sample", "recurrence"])
+    ap.add_argument("kernel", choices=["linear", "attn_decode", "attn_chunk", "experts", "sample", "recurrence", "head_prep"])
     ap.add_argument("--rows", type=int, default=8, help="sample: rows of logits")
     ap.add_argument("--vocab", type=int, default=151936, help="sample: logits of a row")
     ap.add_argument("--one-block", action="store_true", help="sample: never the cluster kernel")
@@ -280,6 +351,7 @@ def main(argv=None) -> int:
     ap.add_argument("--per-group", type=int, default=1, help="recurrence: heads that share q and k")
     ap.add_argument("--ones", action="store_true", help="recurrence: one column more, whose v is 1")
     ap.add_argument("--retention", action="store_true", help="recurrence: the fixed-decay kernels instead")
+    ap.add_argument("--delta", action="store_true", help="recurrence: the gated delta rule instead")
     ap.add_argument("--page-tokens", type=int, default=64)
     ap.add_argument("--window", type=int, default=0)
     ap.add_argument("--experts", type=int, default=60)
@@ -306,7 +378,7 @@ def main(argv=None) -> int:
         print("kernel_bench: no CUDA device", file=sys.stderr)
         return 1
     {"linear": bench_linear, "attn_decode": bench_attn_decode, "attn_chunk": bench_attn_chunk,
-     "experts": bench_experts, "sample": bench_sample, "recurrence": bench_recurrence}[args.kernel](args)
+     "experts": bench_experts, "sample": bench_sample, "recurrence": bench_recurrence, "head_prep": bench_head_prep}[args.kernel](args)
     return 0
 
 

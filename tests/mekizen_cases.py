@@ -236,7 +236,7 @@ def random_config(seed):
             heads = r.choice([1, 2, 4, 8])
             kv = r.choice([k for k in (1, 2, 4, 8) if heads % k == 0])
             dim = r.choice([16, 32, 48, 64, 80, 128])
-            layers.append(with_mlp(attention(heads, kv, dim, r.choice([dim, 32, 64]), window=r.choice([0, 8, 33, 64, 96, 136]),
+            layers.append(with_mlp(attention(heads, kv, dim, r.choice([dim, 32, 64]), window=r.choice([0, 8, 33, 64, 96, 144]),
                                              keep_first=r.choice([0, 2, 6, 20]), rot=r.choice([0, dim // 2, dim]),
                                              base=r.choice([1e4, 5e4]), scale=round(r.uniform(0.05, 0.3), 3)), ff))
             owners.append(i)
