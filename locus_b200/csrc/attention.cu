@@ -456,7 +456,8 @@ __global__ void __launch_bounds__(32 * DS_WARPS, DEEP ? 2 : 4) attn_decode_strea
     // The cut reads only the step's descriptors, which were on the device before the step's first kernel: under
     // programmatic dependent launch it is made while the kernel in front of this one (which writes q and the newest
     // keys and values) still runs; the wait for that kernel comes after it.
-    plan_key_ranges(kr, a.items, a.seg_ctx, a.seg_q0, a.window, n_items, a.nh, max_units, n_warps, cost_range, cost_merge);
+    plan_key_ranges(kr, a.items, a.seg_ctx, a.seg_q0, a.window, n_items, a.nh, max_units, n_warps, cost_range, cost_merge,
+                    a.keep_first);
     bool waited = false;  // whether this warp has waited for the kernel in front (every path does before it leaves)
     int* const s_first = kr.first;
     int* const s_pref = kr.pref;
@@ -490,11 +491,16 @@ __global__ void __launch_bounds__(32 * DS_WARPS, DEEP ? 2 : 4) attn_decode_strea
         const int r = static_cast<int>(u / a.nh);  // range index over the batch
         int item = 0;
         while (s_pref[item + 1] <= r) ++item;  // few items: a linear search
-        const int split = r - s_pref[item];
         const int seg = s_seg[item], p = s_pos[item], row = s_row[item];
-        const int t_lo = a.window > 0 ? max(0, p - a.window + 1) : 0;
-        const int k_begin = s_first[item] + split * len;           // a multiple of 32: chunks do not straddle pages
-        const int k_end = min(p + 1, k_begin + len);               // exclusive
+        // an item's first range may be its kept first tokens (those in front of the window's first chunk); the kept
+        // tokens behind that lie in the window's first chunk and are let through by `seen` below
+        const int kept = kr.kept[item];
+        const bool kept_range = kept > 0 && r == s_pref[item];
+        const int split = r - s_pref[item] - (kept > 0);
+        const int t_lo = kept_range ? 0 : (a.window > 0 ? max(0, p - a.window + 1) : 0);
+        const int k_begin = kept_range ? 0 : s_first[item] + split * len;  // a multiple of 32: chunks do not straddle pages
+        const int k_end = kept_range ? kept : min(p + 1, k_begin + len);   // exclusive
+        const int keep = a.keep_first;
         const int kvh = h / (a.nh / a.nkv);
         const int* table = a.block_table + static_cast<size_t>(seg) * a.table_stride;
         const T* pool = static_cast<const T*>(a.pool) + static_cast<size_t>(kvh) * P * hd + d0;
@@ -517,11 +523,11 @@ __global__ void __launch_bounds__(32 * DS_WARPS, DEEP ? 2 : 4) attn_decode_strea
         };
         auto live = [&](int k0, int g) -> bool {
             const int t = k0 + g * KPL + grp;
-            return active && t >= t_lo && t < k_end;
+            return active && (t >= t_lo || t < keep) && t < k_end;
         };
         auto t_live = [&](int k0, int g) -> bool {  // the key itself, whatever this lane's part of its row
             const int t = k0 + g * KPL + grp;
-            return t >= t_lo && t < k_end;
+            return (t >= t_lo || t < keep) && t < k_end;
         };
         const uint4 zero4 = make_uint4(0, 0, 0, 0);
         float q[VEC];
@@ -827,15 +833,15 @@ extern "C" int locus_attn_decode(const void* q, int dt, const void* pool, void* 
                            nh, nkv, hd, page_tokens, window, scale, keep_first, sink);
     a.part_o = part_o; a.part_ml = part_ml; a.counters = counters; a.max_splits = max_splits;
     if (counters == nullptr) return LOCUS_ERR_UNSUPPORTED;
-    if (max_units < static_cast<long long>(n_items) * nh) return LOCUS_ERR_UNSUPPORTED;
+    // (one partial result per request and head at least; two where kept first tokens are a range of their own)
+    if (max_units < static_cast<long long>(n_items) * nh * (a.keep_first > 0 ? 2 : 1)) return LOCUS_ERR_UNSUPPORTED;
     // rows of 64 to 512 bytes: the streaming kernel on a fixed grid, 8, 16 or 32 lanes to a row (the row's 16-byte
     // pieces rounded up to a power of two: a head of 96 bfloat16 elements takes 12 of 16 lanes)
     const int pieces = hd * (dt == LOCUS_DT_F32 ? 4 : 2) / 16;
     const int lpk = pieces < 4 ? 0 : pieces <= 8 ? 8 : pieces <= 16 ? 16 : pieces <= 32 ? 32 : 0;
     const int chunk_keys = lpk > 0 ? DS_LOADS * 32 / lpk : 1;
-    // (a window that keeps first tokens: the split kernel below, whose fixed ranges of positions hold them as they are)
     if ((dt == LOCUS_DT_F32 || dt == LOCUS_DT_BF16) && lpk > 0 && n_items <= DS_MAX_ITEMS &&
-        page_tokens % chunk_keys == 0 && a.keep_first == 0) {
+        page_tokens % chunk_keys == 0) {
         static int n_sm = 0;
         if (n_sm == 0) {
             int dev = 0;

@@ -42,6 +42,7 @@ struct GqaArgs {
     int table_stride;
     const int* items;         // [n_items] segments with one new token
     int nh, nkv, page_tokens, window;
+    int keep_first, sink;     // with a window: a request's first tokens stay in sight; one more term of score 0 in the denominator
     float scale;
     float* part_o;            // [units * G][hd]
     float* part_ml;           // [units * G][2]
@@ -176,7 +177,7 @@ __global__ void __launch_bounds__(32 * GQW, 1) attn_decode_gqa_kernel(GqaArgs a,
     const int n_warps = gridDim.x * GQW;
     // a unit (range, kv head) leaves G partial results: the scratch holds max_units of them
     const int len = plan_key_ranges(kr, a.items, a.seg_ctx, a.seg_q0, a.window, n_items, a.nkv, max_units / G, n_warps,
-                                    cost_range, cost_merge);
+                                    cost_range, cost_merge, a.keep_first);
     // (the cut read only the step's descriptors; q and the newest keys and values come from the kernel in front)
     pdl_entry();
     if (len == 0) return;
@@ -190,11 +191,15 @@ __global__ void __launch_bounds__(32 * GQW, 1) attn_decode_gqa_kernel(GqaArgs a,
         const int r = static_cast<int>(u / a.nkv);
         int item = 0;
         while (kr.pref[item + 1] <= r) ++item;
-        const int split = r - kr.pref[item];
         const int seg = kr.seg[item], p = kr.pos[item], row = kr.row[item];
-        const int t_lo = a.window > 0 ? max(0, p - a.window + 1) : 0;
-        const int k_begin = kr.first[item] + split * len;   // a multiple of 32
-        const int k_end = min(p + 1, k_begin + len);        // exclusive
+        // an item's first range may be its kept first tokens (those in front of the window's first 32 keys); kept tokens
+        // behind that lie in the window's first range, in front of the window's start, and are live there
+        const int kept = kr.kept[item], keep = a.keep_first;
+        const bool kept_range = kept > 0 && r == kr.pref[item];
+        const int split = r - kr.pref[item] - (kept > 0);
+        const int t_lo = kept_range ? 0 : (a.window > 0 ? max(0, p - a.window + 1) : 0);
+        const int k_begin = kept_range ? 0 : kr.first[item] + split * len;   // a multiple of 32
+        const int k_end = kept_range ? kept : min(p + 1, k_begin + len);      // exclusive
         const int* table = a.block_table + static_cast<size_t>(seg) * a.table_stride;
         const bf16* pool_kv = a.pool + static_cast<size_t>(kvh) * P * HD;
 
@@ -240,7 +245,9 @@ __global__ void __launch_bounds__(32 * GQW, 1) attn_decode_gqa_kernel(GqaArgs a,
             }
         };
         // the first chunk that holds a live key (a window may start up to 31 keys into the range's first 32)
-        const int k_start = max(k_begin, t_lo & ~15);
+        // (with a kept token at the range's start the chunk in front of the window's start is read too: it holds one,
+        // so its page is the request's; no chunk without a live key is ever fetched)
+        const int k_start = keep > k_begin ? k_begin : max(k_begin, t_lo & ~15);
         bool ok = true;
 #pragma unroll
         for (int c = 0; c < GQS - 1; ++c) issue(k_start + 16 * c, c);
@@ -262,7 +269,7 @@ __global__ void __launch_bounds__(32 * GQW, 1) attn_decode_gqa_kernel(GqaArgs a,
             if (k0 < t_lo || k0 + 16 > k_end) {
                 // a chunk with dead keys: their V rows become zeros (two lanes per row, 8 x 16 bytes of its 2 hd each)
                 const int r = lane >> 1, t = k0 + r;
-                if (t < t_lo || t >= k_end) {
+                if ((t < t_lo && t >= keep) || t >= k_end) {
 #pragma unroll
                     for (int x = 0; x < ROW_BYTES / 32; ++x) sts16_zero(src + TILE_BYTES + r * ROW_BYTES + (lane & 1) * (ROW_BYTES / 2) + 16 * x);
                 }
@@ -283,7 +290,8 @@ __global__ void __launch_bounds__(32 * GQW, 1) attn_decode_gqa_kernel(GqaArgs a,
 #pragma unroll
                 for (int i = 0; i < VL; ++i) vreg[kk][i] = lds16(src + TILE_BYTES + r * ROW_BYTES + (gq + 8 * i) * 16);
             }
-            const bool live_lo = k0 + gq >= t_lo && k0 + gq < k_end, live_hi = k0 + 8 + gq >= t_lo && k0 + 8 + gq < k_end;
+            const bool live_lo = (k0 + gq >= t_lo || k0 + gq < keep) && k0 + gq < k_end;
+            const bool live_hi = (k0 + 8 + gq >= t_lo || k0 + 8 + gq < keep) && k0 + 8 + gq < k_end;
             uint32_t pb[HT][2];
 #pragma unroll
             for (int ht = 0; ht < HT; ++ht) {
@@ -414,7 +422,8 @@ __global__ void __launch_bounds__(32 * GQW, 1) attn_decode_gqa_kernel(GqaArgs a,
                     acc1.x = fmaf(v1.x, w1, acc1.x); acc1.y = fmaf(v1.y, w1, acc1.y);
                     acc1.z = fmaf(v1.z, w1, acc1.z); acc1.w = fmaf(v1.w, w1, acc1.w);
                 }
-                const float inv0 = 1.0f / L0, inv1 = 1.0f / L1;
+                // (the sink: one more term of score 0; scores are in base 2 here)
+                const float inv0 = 1.0f / (a.sink ? L0 + exp2f(-M0) : L0), inv1 = 1.0f / (a.sink ? L1 + exp2f(-M1) : L1);
                 bf16* dst = a.out + (static_cast<size_t>(row) * a.nh + static_cast<size_t>(kvh) * G + g) * HD + d;
                 dst[0] = from_f<bf16>(acc0.x * inv0);
                 dst[1] = from_f<bf16>(acc0.y * inv0);
@@ -450,11 +459,14 @@ extern "C" int locus_attn_decode_gqa(const void* q, const void* pool, void* out,
                                      const int* block_table, int table_stride, const int* items, int n_items, int nh,
                                      int nkv, int hd, int page_tokens, int window, float scale, float* part_o,
                                      float* part_ml, int* counters, long long max_units, int cost_range,
-                                     int cost_merge, cudaStream_t stream) {
+                                     int cost_merge, int keep_first, int sink, cudaStream_t stream) {
     if (n_items <= 0) return 0;
     if (!locus_attn_decode_gqa_takes(LOCUS_DT_BF16, nh, nkv, hd, page_tokens, n_items) || window < 0 || counters == nullptr)
         return LOCUS_ERR_UNSUPPORTED;
-    if (max_units < static_cast<long long>(n_items) * nh) return LOCUS_ERR_UNSUPPORTED;
+    if (keep_first < 0) return LOCUS_ERR_UNSUPPORTED;
+    if (window == 0) keep_first = 0;
+    // (one partial result per request and head at least; two where kept first tokens are a range of their own)
+    if (max_units < static_cast<long long>(n_items) * nh * (keep_first > 0 ? 2 : 1)) return LOCUS_ERR_UNSUPPORTED;
     static int n_sm = 0;
     if (n_sm == 0) {
         int dev = 0;
@@ -470,6 +482,7 @@ extern "C" int locus_attn_decode_gqa(const void* q, const void* pool, void* out,
     a.out = static_cast<bf16*>(out);
     a.seg_q0 = seg_q0; a.seg_ctx = seg_ctx; a.block_table = block_table; a.table_stride = table_stride; a.items = items;
     a.nh = nh; a.nkv = nkv; a.page_tokens = page_tokens; a.window = window; a.scale = scale;
+    a.keep_first = keep_first; a.sink = sink;
     a.part_o = part_o; a.part_ml = part_ml; a.counters = counters;
     const dim3 grid(n_sm);
     const bool wide = nh / nkv > 8;

@@ -47,6 +47,7 @@ struct TcAttnArgs {
     int table_stride;
     const int* items;
     int nh, nkv, page_tokens, window;
+    int keep_first, sink;   // with a window: a request's first tokens stay in sight; one more term of score 0 in the denominator
     float scale;
     // Ranges of key tiles per block of queries (1: a block writes the result itself).  With more, a block takes
     // one range (blockIdx.z) and leaves, per query row of the step and head, its unnormalised sum, its running
@@ -56,14 +57,17 @@ struct TcAttnArgs {
     float* part_ml;   // [row][head][split][2]
 };
 
-// Key tiles of a block of nq queries whose first sits at position p0: the first tile's first position and their
-// number, and how they are cut into ranges (the same in both kernels).
-__device__ __forceinline__ void at_tiles(int p0, int nq, int window, int n_splits, int& first_tile, int& n_tiles,
-                                         int& per_split) {
+// Key tiles of a block of nq queries whose first sits at position p0: first the n_keep tiles of the kept first
+// tokens that lie wholly in front of the window's first tile (tile j at position j * AT_MK), then the window's
+// (tile j at first_tile + (j - n_keep) * AT_MK); their number, and how they are cut into ranges (the same in both
+// kernels).
+__device__ __forceinline__ void at_tiles(int p0, int nq, int window, int keep_first, int n_splits, int& first_tile,
+                                         int& n_keep, int& n_tiles, int& per_split) {
     const int t_hi = p0 + nq - 1;
     const int t_lo = window > 0 ? max(0, p0 - window + 1) : 0;
     first_tile = (t_lo / AT_MK) * AT_MK;
-    n_tiles = (t_hi - first_tile) / AT_MK + 1;
+    n_keep = (window > 0 && keep_first > 0) ? min((keep_first + AT_MK - 1) / AT_MK, first_tile / AT_MK) : 0;
+    n_tiles = n_keep + (t_hi - first_tile) / AT_MK + 1;
     per_split = (n_tiles + n_splits - 1) / n_splits;
 }
 
@@ -233,12 +237,17 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     const int t_lo = a.window > 0 ? max(0, p0 - a.window + 1) : 0;
     const int P = a.page_tokens;
     // this block's range of the key tiles (all of them when the keys are not cut)
-    int first_tile, n_tiles_all, per_split;
-    at_tiles(p0, nq, a.window, a.n_splits, first_tile, n_tiles_all, per_split);
+    int first_tile, n_keep, n_tiles_all, per_split;
+    at_tiles(p0, nq, a.window, a.keep_first, a.n_splits, first_tile, n_keep, n_tiles_all, per_split);
     const int split = blockIdx.z;
-    first_tile += split * per_split * AT_MK;
-    const int n_tiles = max(0, min(per_split, n_tiles_all - split * per_split));
+    const int j0 = split * per_split;  // this block's first tile in the list of all
+    const int n_tiles = max(0, min(per_split, n_tiles_all - j0));
     if (n_tiles == 0) return;  // the merge counts the live ranges the same way
+    const int keep = a.window > 0 ? a.keep_first : 0;
+    auto tile_at = [&](int j) -> int {  // first position of this block's tile j
+        const int jj = j0 + j;
+        return jj < n_keep ? jj * AT_MK : first_tile + (jj - n_keep) * AT_MK;
+    };
     const int* table = a.block_table + static_cast<size_t>(seg) * a.table_stride;
 
     // shared memory: Q, K[2], V[2], P[2] (each a tile of two swizzled halves), then the barriers.  That is
@@ -291,14 +300,14 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             for (int j = 0; j < n_tiles; ++j) {
                 const int b = j & 1;
                 const uint32_t par = ((j >> 1) & 1) ^ 1;
-                const int tile0 = first_tile + j * AT_MK;
+                const int tile0 = tile_at(j);
                 // rows of the pool (viewed as [pages * 2 * nkv * P][hd]) of the two 64-key halves; a half with
                 // no page, or wholly outside the keys this block may see, is fetched from outside the tensor
                 int krow[2];
                 for (int hh = 0; hh < 2; ++hh) {
                     const int t = tile0 + 64 * hh;
                     int page = -1;
-                    if (t <= t_hi && t + 63 >= t_lo) page = table[t / P];
+                    if (t <= t_hi && (t + 63 >= t_lo || t < keep)) page = table[t / P];
                     krow[hh] = page < 0 ? -64 : static_cast<int>(page * rows_per_page + static_cast<long long>(kvh) * P + t % P);
                 }
                 const int v_shift = a.nkv * P;  // V rows of a page lie nkv * P rows behind its K rows
@@ -383,15 +392,16 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         // the two warps of a row meet at every one of their barriers.)
         for (int j = 0; j < n_tiles; ++j) {
             const int b = j & 1;
-            const int tile0 = first_tile + j * AT_MK + 64 * half;  // first key of this thread's half of the tile
+            const int tile_first = tile_at(j);
+            const int tile0 = tile_first + 64 * half;  // first key of this thread's half of the tile
             if (!at_wait(s_full + 8 * b, (j >> 1) & 1, 10)) ok = false;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             uint32_t s0[32], s1[32];
             at_ld32(tS + b * AT_MK + lane_bits + 64 * half, s0);
             at_ld32(tS + b * AT_MK + lane_bits + 64 * half + 32, s1);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            // a key t counts for this row when lo <= t <= pq; only tiles at an edge need the test
-            const int tile_first = first_tile + j * AT_MK;
+            // a key t counts for this row when lo <= t <= pq, or when it is one of the kept first tokens; only tiles
+            // at an edge need the test (a tile of kept tokens lies in front of t_lo, so it is always tested)
             const bool need_mask = tile_first + AT_MK - 1 > p0 || tile_first < t_lo ||
                                    (a.window > 0 && tile_first <= p0 + AT_MQ - 1 - a.window);
             float mx = -INFINITY;
@@ -399,8 +409,8 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
                     const int t = tile0 + i;
-                    if (!(t <= pq && t >= lo)) s0[i] = 0xff800000u;            // -inf
-                    if (!(t + 32 <= pq && t + 32 >= lo)) s1[i] = 0xff800000u;
+                    if (!(t <= pq && (t >= lo || t < keep))) s0[i] = 0xff800000u;            // -inf
+                    if (!(t + 32 <= pq && (t + 32 >= lo || t + 32 < keep))) s1[i] = 0xff800000u;
                 }
             }
 #pragma unroll
@@ -492,7 +502,8 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         {
             const float l = l_run + with_partner(n_tiles & 1, l_run);
-            const float inv = 1.0f / l;
+            // the sink: one more term of score 0 (the sums are relative to 2^m_run); with ranges, the merge adds it
+            const float inv = 1.0f / (a.sink && a.n_splits == 1 ? l + exp2f(-m_run) : l);
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
                 uint32_t v[32];
@@ -544,8 +555,8 @@ __global__ void __launch_bounds__(128) attn_chunk_tc_merge_kernel(TcAttnArgs a) 
     if (i >= nq * (AT_HD / 4)) return;
     const int r = i / (AT_HD / 4), d = (i - r * (AT_HD / 4)) * 4;
     const int row = a.seg_q0[seg] + qoff + r;
-    int first_tile, n_tiles, per_split;
-    at_tiles(a.seg_ctx[seg] + qoff, nq, a.window, a.n_splits, first_tile, n_tiles, per_split);
+    int first_tile, n_keep, n_tiles, per_split;
+    at_tiles(a.seg_ctx[seg] + qoff, nq, a.window, a.keep_first, a.n_splits, first_tile, n_keep, n_tiles, per_split);
     const int live = (n_tiles + per_split - 1) / per_split;
     const size_t unit0 = (static_cast<size_t>(row) * a.nh + h) * a.n_splits;
     float2 ml[AT_MAX_SPLITS];
@@ -573,6 +584,7 @@ __global__ void __launch_bounds__(128) attn_chunk_tc_merge_kernel(TcAttnArgs a) 
         acc.z += v[s].z * w;
         acc.w += v[s].w * w;
     }
+    if (a.sink) L += exp2f(-M);
     const float inv = 1.0f / L;
     uint2 pk;
     pk.x = at_pack(acc.x * inv, acc.y * inv);
@@ -621,13 +633,13 @@ extern "C" int locus_attn_chunk_tc(const void* q, long long T, const void* pool,
                                    const int* seg_q0, const int* seg_qn, const int* seg_ctx, const int* block_table,
                                    int table_stride, const int* items, int n_items, int nh, int nkv, int hd,
                                    int page_tokens, int window, float scale, int n_splits, float* part_o,
-                                   float* part_ml, cudaStream_t stream) {
+                                   float* part_ml, int keep_first, int sink, cudaStream_t stream) {
     if (n_items <= 0) return 0;
     if (n_splits < 1 || n_splits > AT_MAX_SPLITS) return LOCUS_ERR_UNSUPPORTED;
     if (n_splits > 1 && (part_o == nullptr || part_ml == nullptr ||
                          ((reinterpret_cast<uintptr_t>(part_o) | reinterpret_cast<uintptr_t>(part_ml)) & 15)))
         return LOCUS_ERR_UNSUPPORTED;
-    if (hd != AT_HD || page_tokens <= 0 || page_tokens % 64 != 0 || window < 0) return LOCUS_ERR_UNSUPPORTED;
+    if (hd != AT_HD || page_tokens <= 0 || page_tokens % 64 != 0 || window < 0 || keep_first < 0) return LOCUS_ERR_UNSUPPORTED;
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || nh > 65535) return LOCUS_ERR_UNSUPPORTED;
     const long long pool_rows = n_pages * 2 * nkv * page_tokens;
     if (T <= 0 || n_pages <= 0 || pool_rows >= (1LL << 31) || T >= (1LL << 31)) return LOCUS_ERR_UNSUPPORTED;
@@ -641,6 +653,7 @@ extern "C" int locus_attn_chunk_tc(const void* q, long long T, const void* pool,
     a.out = static_cast<bf16*>(out); a.seg_q0 = seg_q0; a.seg_qn = seg_qn; a.seg_ctx = seg_ctx;
     a.block_table = block_table; a.table_stride = table_stride; a.items = items; a.nh = nh; a.nkv = nkv;
     a.page_tokens = page_tokens; a.window = window; a.scale = scale;
+    a.keep_first = window > 0 ? keep_first : 0; a.sink = sink ? 1 : 0;
     a.n_splits = n_splits; a.part_o = part_o; a.part_ml = part_ml;
     const size_t smem = 7 * AT_TILE_BYTES + 160 + 2 * 2 * 128 * 4;
     static bool set = false;

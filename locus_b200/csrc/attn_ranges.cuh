@@ -10,6 +10,7 @@
 struct KeyRanges {
     int first[DS_MAX_ITEMS];     // first key of item i, rounded down to 32
     int nkeys[DS_MAX_ITEMS];     // keys from there to the query's own position
+    int kept[DS_MAX_ITEMS];      // a window that keeps first tokens: those in front of `first` (one more range, the item's first)
     int pref[DS_MAX_ITEMS + 1];  // ranges of the items before i
     int seg[DS_MAX_ITEMS], pos[DS_MAX_ITEMS], row[DS_MAX_ITEMS];  // segment, position, row of q / out
     unsigned long long best[32];
@@ -19,11 +20,13 @@ struct KeyRanges {
 // Fills `kr` (all threads of the block take part; ends with a barrier) and returns the range length in keys,
 // 0 when not even one range per (request, unit) fits max_units.  `per_range`: units of work per range of keys
 // (query heads, or key/value heads when a warp serves a whole group); cost of a cut = rounds over the grid's
-// n_warps warps x (range length + cost_range) + cost_merge x ranges of the longest request.
+// n_warps warps x (range length + cost_range) + cost_merge x ranges of the longest request.  keep_first > 0 (with a
+// window): the request's first keep_first tokens stay in sight; those in front of the window's first chunk are one
+// more range of the item, in front of the others (kr.kept keys from position 0; the caller walks it like any other).
 __device__ __forceinline__ int plan_key_ranges(KeyRanges& kr, const int* __restrict__ items,
                                                const int* __restrict__ seg_ctx, const int* __restrict__ seg_q0,
                                                int window, int n_items, int per_range, long long max_units,
-                                               int n_warps, int cost_range, int cost_merge) {
+                                               int n_warps, int cost_range, int cost_merge, int keep_first = 0) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, n_block_warps = blockDim.x >> 5;
     int longest = 0;
     for (int i = tid; i < n_items; i += blockDim.x) {
@@ -33,6 +36,7 @@ __device__ __forceinline__ int plan_key_ranges(KeyRanges& kr, const int* __restr
         const int first = t_lo & ~31;
         kr.first[i] = first;
         kr.nkeys[i] = p - first + 1;
+        kr.kept[i] = window > 0 ? min(keep_first, first) : 0;
         kr.seg[i] = seg;
         kr.pos[i] = p;
         kr.row[i] = seg_q0[seg];
@@ -46,7 +50,7 @@ __device__ __forceinline__ int plan_key_ranges(KeyRanges& kr, const int* __restr
         const int len = step * (c + 1);
         if (len - step >= longest && c > 0) break;  // longer than any context: same cut as the one before
         long long units = 0;
-        for (int i = 0; i < n_items; ++i) units += (kr.nkeys[i] + len - 1) / len;
+        for (int i = 0; i < n_items; ++i) units += (kr.nkeys[i] + len - 1) / len + (kr.kept[i] > 0);
         units *= per_range;
         if (units > max_units) continue;  // the scratch does not hold that many partial results
         const long long rounds = (units + n_warps - 1) / n_warps;
@@ -68,7 +72,7 @@ __device__ __forceinline__ int plan_key_ranges(KeyRanges& kr, const int* __restr
         const int len = max(32, kr.len);
         for (int i = 0; i < n_items; ++i) {
             kr.pref[i] = acc;
-            acc += (kr.nkeys[i] + len - 1) / len;
+            acc += (kr.nkeys[i] + len - 1) / len + (kr.kept[i] > 0);
         }
         kr.pref[n_items] = acc;
     }

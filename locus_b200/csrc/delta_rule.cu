@@ -8,11 +8,22 @@
 // q, k and v are columns of float32 row matrices given by pointer, row stride and offset.
 //
 // The columns of S do not meet: with a = S_old^T k, b = S_old^T q (both of the state BEFORE the token) and the number
-// k . q, u = beta (v - g a) and o = g b + u (k . q).  So a token costs one round of warp sums, not two in a row.
+// k . q, u = beta (v - g a) and o = g b + u (k . q).  So a token costs one round of sums across lanes, not two in a row.
 //
-//   delta_scan   a warp owns DR_CW columns of one head's state for one request and walks the request's new tokens in
-//                order; lane l keeps the rows l, l + 32, ... of its columns in registers (d <= 256).  The order of
-//                every sum is fixed by d alone, so a cut of a prompt changes nothing at all.
+//   delta_scan   a warp owns DR_CW = 4 columns of one head's state for one request and walks the request's new tokens
+//                in order.  Its lanes are 8 groups of rows x 4 columns: lane (lr, lc) keeps, of column lc, the rows
+//                32 j + 4 lr + {0, 1, 2, 3} (j = 0, 1, ...; d <= 256) in registers, so that the three sums of a token
+//                (a, b and k . q) cross 8 lanes in three exchanges each -- nine shuffles a token and warp, where a
+//                lane that kept rows l, l + 32, ... of all four columns needed forty-five: with many requests the
+//                shuffle unit, one warp instruction a cycle and SM, was the limit.  The four rows are one 16-byte load
+//                of k and of q where the operands allow it, and the 8 row groups read one 128-byte line.  The next
+//                token's operands are fetched while this one is worked on.  The order of every sum is fixed by d
+//                alone, so a cut of a prompt changes nothing at all.
+//                Where every operand allows 16-byte copies (RING) each warp keeps a ring of the next tokens' operands
+//                in shared memory, filled by asynchronous copies several tokens ahead: a token's sums and exchanges
+//                take a fraction of a load's way to L2 and back, and with four warps or fewer on an SM (one request,
+//                16 heads) one token fetched ahead left the walk waiting on memory most of the time.  The registers
+//                are then filled from the ring one token ahead as before; the arithmetic is the same.
 //   delta_out    a head's read-out divided by its root mean square, times a weight, times silu(gate).
 #include "common.cuh"
 
@@ -34,95 +45,166 @@ struct DeltaArgs {
     int H, heads_per_group, d, dv;
 };
 
-template <int RPL>
+// R: rows of a column that a lane keeps (d <= 8 R).  VEC: q's and k's rows of a head start on 16-byte boundaries and d
+// is a multiple of 4, so four rows are one load.
+// One stage of a warp's ring: q and k (8 R rows each), then v's four columns, beta and the decay.
+#define DR_STAGE(R) (16 * (R) + 8)
+
+__device__ __forceinline__ void dr_copy16(float* dst, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(static_cast<unsigned>(__cvta_generic_to_shared(dst))), "l"(src)
+                 : "memory");
+}
+__device__ __forceinline__ void dr_copy4(float* dst, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(static_cast<unsigned>(__cvta_generic_to_shared(dst))), "l"(src)
+                 : "memory");
+}
+__device__ __forceinline__ void dr_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void dr_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// RING (implies VEC; v's four columns of a warp are one aligned 16-byte piece too): NST stages per warp.
+template <int R, bool VEC, bool RING, int NST>
 __global__ void __launch_bounds__(128) delta_scan_kernel(const DeltaArgs a, int col_groups) {
     pdl_entry();
     pdl_trigger();
-    const int lane = threadIdx.x & 31;
+    __shared__ __align__(16) float ring_all[RING ? 4 * NST * DR_STAGE(R) : 4];
+    float* const ring = ring_all + (RING ? (threadIdx.x >> 5) * NST * DR_STAGE(R) : 0);
+    const int lane = threadIdx.x & 31, lr = lane >> 2, lc = lane & 3;
     const int unit = blockIdx.x * 4 + (threadIdx.x >> 5);  // (head, column group)
     const int seg = blockIdx.y;
     if (unit >= a.H * col_groups) return;
     const int qn = a.seg_qn[seg];
-    const int h = unit / col_groups, c0 = (unit % col_groups) * DR_CW;
+    const int h = unit / col_groups, col = (unit % col_groups) * DR_CW + lc;
     const int d = a.d, dv = a.dv, q0 = a.seg_q0[seg];
+    const bool col_ok = col < dv;
     float* S = a.state + static_cast<size_t>(a.state_slots[seg]) * a.slot_stride + static_cast<size_t>(h) * d * dv;
-    float s[RPL][DR_CW];
+    auto row_of = [&](int i) { return 32 * (i >> 2) + 4 * lr + (i & 3); };
+    float s[R];
 #pragma unroll
-    for (int r = 0; r < RPL; ++r) {
-        const int i = lane + 32 * r;
-#pragma unroll
-        for (int c = 0; c < DR_CW; ++c) s[r][c] = (i < d && c0 + c < dv) ? S[static_cast<size_t>(i) * dv + c0 + c] : 0.f;
+    for (int i = 0; i < R; ++i) {
+        const int r = row_of(i);
+        s[i] = (r < d && col_ok) ? S[static_cast<size_t>(r) * dv + col] : 0.f;
     }
     const int g = h / a.heads_per_group;
     const int off_q = a.off_q + g * d, off_k = a.off_k + g * d, off_v = a.off_v + h * dv;
-    float qn_[RPL], kn_[RPL], vn_[DR_CW], beta_n = 0.f, decay_n = 0.f;
-    auto fetch = [&](int t) {
-        const size_t row = static_cast<size_t>(q0 + t);
-#pragma unroll
-        for (int r = 0; r < RPL; ++r) {
-            const int i = lane + 32 * r;
-            qn_[r] = i < d ? a.q[row * a.ldq + off_q + i] : 0.f;
-            kn_[r] = i < d ? a.k[row * a.ldk + off_k + i] : 0.f;
+    float qn_[R], kn_[R], vn_ = 0.f, beta_n = 0.f, decay_n = 0.f;
+    // token t's operands on their way into its stage of the ring; one group of copies per token, empty behind the last
+    auto stage_in = [&](int t) {
+        if (t < qn) {
+            float* st = ring + (t % NST) * DR_STAGE(R);
+            const size_t row = static_cast<size_t>(q0 + t);
+            const float* qp = a.q + row * a.ldq + off_q;
+            const float* kp = a.k + row * a.ldk + off_k;
+            for (int i = lane; 4 * i < d; i += 32) {
+                dr_copy16(st + 4 * i, qp + 4 * i);
+                dr_copy16(st + 8 * R + 4 * i, kp + 4 * i);
+            }
+            if (lane == 0) dr_copy16(st + 16 * R, a.v + row * a.ldv + off_v + (col - lc));
+            if (lane == 1) dr_copy4(st + 16 * R + 4, a.beta + row * a.H + h);
+            if (lane == 2) dr_copy4(st + 16 * R + 5, a.decay + row * a.H + h);
         }
+        dr_commit();
+    };
+    auto fetch = [&](int t) {
+        if (RING) {
+            // the groups of tokens up to t + NST - 2 are committed: all but the newest NST - 2 have landed, so has
+            // token t's; the barrier makes the other lanes' copies visible and orders this read behind the reads of
+            // the stage that the next copy overwrites
+            dr_wait<NST - 2>();
+            __syncwarp();
+            const float* st = ring + (t % NST) * DR_STAGE(R);
 #pragma unroll
-        for (int c = 0; c < DR_CW; ++c) vn_[c] = c0 + c < dv ? a.v[row * a.ldv + off_v + c0 + c] : 0.f;
+            for (int j = 0; j < R / 4; ++j) {
+                const int r = 32 * j + 4 * lr;
+                float4 qv = make_float4(0.f, 0.f, 0.f, 0.f), kv = qv;
+                if (r < d) {
+                    qv = *reinterpret_cast<const float4*>(st + r);
+                    kv = *reinterpret_cast<const float4*>(st + 8 * R + r);
+                }
+                qn_[4 * j] = qv.x; qn_[4 * j + 1] = qv.y; qn_[4 * j + 2] = qv.z; qn_[4 * j + 3] = qv.w;
+                kn_[4 * j] = kv.x; kn_[4 * j + 1] = kv.y; kn_[4 * j + 2] = kv.z; kn_[4 * j + 3] = kv.w;
+            }
+            vn_ = st[16 * R + lc];
+            beta_n = st[16 * R + 4];
+            decay_n = st[16 * R + 5];
+            return;
+        }
+        const size_t row = static_cast<size_t>(q0 + t);
+        const float* qp = a.q + row * a.ldq + off_q;
+        const float* kp = a.k + row * a.ldk + off_k;
+        if (VEC) {
+#pragma unroll
+            for (int j = 0; j < R / 4; ++j) {
+                const int r = 32 * j + 4 * lr;
+                float4 qv = make_float4(0.f, 0.f, 0.f, 0.f), kv = qv;
+                if (r < d) {
+                    qv = *reinterpret_cast<const float4*>(qp + r);
+                    kv = *reinterpret_cast<const float4*>(kp + r);
+                }
+                qn_[4 * j] = qv.x; qn_[4 * j + 1] = qv.y; qn_[4 * j + 2] = qv.z; qn_[4 * j + 3] = qv.w;
+                kn_[4 * j] = kv.x; kn_[4 * j + 1] = kv.y; kn_[4 * j + 2] = kv.z; kn_[4 * j + 3] = kv.w;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < R; ++i) {
+                const int r = row_of(i);
+                qn_[i] = r < d ? qp[r] : 0.f;
+                kn_[i] = r < d ? kp[r] : 0.f;
+            }
+        }
+        vn_ = col_ok ? a.v[row * a.ldv + off_v + col] : 0.f;
         beta_n = a.beta[row * a.H + h];
         decay_n = a.decay[row * a.H + h];
     };
+    if (RING) {
+#pragma unroll 1
+        for (int t = 0; t < NST - 1; ++t) stage_in(t);
+    }
     if (qn > 0) fetch(0);
     for (int t = 0; t < qn; ++t) {
-        float qq[RPL], kk[RPL], vv[DR_CW];
-        const float beta = beta_n, gd = decay_n;
+        float qq[R], kk[R];
+        const float beta = beta_n, gd = decay_n, vv = vn_;
 #pragma unroll
-        for (int r = 0; r < RPL; ++r) {
-            qq[r] = qn_[r];
-            kk[r] = kn_[r];
+        for (int i = 0; i < R; ++i) {
+            qq[i] = qn_[i];
+            kk[i] = kn_[i];
         }
-#pragma unroll
-        for (int c = 0; c < DR_CW; ++c) vv[c] = vn_[c];
+        if (RING) stage_in(t + NST - 1);  // into the stage that token t - 1 left (read one iteration ago, a barrier since)
         if (t + 1 < qn) fetch(t + 1);  // the next token's operands are on their way while this one is worked on
-        float sk[DR_CW], sq[DR_CW], kq = 0.f;
+        // two partial sums each: a chain of R dependent additions is as long as the exchanges behind it
+        float sk0 = 0.f, sk1 = 0.f, sq0 = 0.f, sq1 = 0.f, kq0 = 0.f, kq1 = 0.f;
 #pragma unroll
-        for (int c = 0; c < DR_CW; ++c) sk[c] = sq[c] = 0.f;
-#pragma unroll
-        for (int r = 0; r < RPL; ++r) {
-            kq = fmaf(kk[r], qq[r], kq);
-#pragma unroll
-            for (int c = 0; c < DR_CW; ++c) {
-                sk[c] = fmaf(s[r][c], kk[r], sk[c]);
-                sq[c] = fmaf(s[r][c], qq[r], sq[c]);
-            }
+        for (int i = 0; i < R; i += 2) {
+            sk0 = fmaf(s[i], kk[i], sk0);
+            sq0 = fmaf(s[i], qq[i], sq0);
+            kq0 = fmaf(kk[i], qq[i], kq0);
+            sk1 = fmaf(s[i + 1], kk[i + 1], sk1);
+            sq1 = fmaf(s[i + 1], qq[i + 1], sq1);
+            kq1 = fmaf(kk[i + 1], qq[i + 1], kq1);
         }
-        kq = warp_sum(kq);
-        float u[DR_CW], o[DR_CW];
+        float sk = sk0 + sk1, sq = sq0 + sq1, kq = kq0 + kq1;
 #pragma unroll
-        for (int c = 0; c < DR_CW; ++c) {
-            sk[c] = warp_sum(sk[c]);
-            sq[c] = warp_sum(sq[c]);
-            u[c] = beta * (vv[c] - gd * sk[c]);
-            o[c] = fmaf(u[c], kq, gd * sq[c]);
+        for (int m = 4; m < 32; m <<= 1) {  // across the 8 row groups of this column
+            sk += __shfl_xor_sync(0xffffffffu, sk, m);
+            sq += __shfl_xor_sync(0xffffffffu, sq, m);
+            kq += __shfl_xor_sync(0xffffffffu, kq, m);
         }
+        const float u = beta * (vv - gd * sk);
+        const float o = fmaf(u, kq, gd * sq);
 #pragma unroll
-        for (int r = 0; r < RPL; ++r) {
-#pragma unroll
-            for (int c = 0; c < DR_CW; ++c) s[r][c] = fmaf(gd, s[r][c], kk[r] * u[c]);
-        }
-        if (lane < DR_CW && c0 + lane < dv) {
-            float ov = o[0];
-#pragma unroll
-            for (int c = 1; c < DR_CW; ++c)
-                if (lane == c) ov = o[c];
-            a.out[static_cast<size_t>(q0 + t) * a.ldo + h * dv + c0 + lane] = ov;
-        }
+        for (int i = 0; i < R; ++i) s[i] = fmaf(gd, s[i], kk[i] * u);
+        if (lr == 0 && col_ok) a.out[static_cast<size_t>(q0 + t) * a.ldo + h * dv + col] = o;
     }
 #pragma unroll
-    for (int r = 0; r < RPL; ++r) {
-        const int i = lane + 32 * r;
-#pragma unroll
-        for (int c = 0; c < DR_CW; ++c)
-            if (i < d && c0 + c < dv) S[static_cast<size_t>(i) * dv + c0 + c] = s[r][c];
+    for (int i = 0; i < R; ++i) {
+        const int r = row_of(i);
+        if (r < d && col_ok) S[static_cast<size_t>(r) * dv + col] = s[i];
     }
 }
+
+static int g_dr_ring = 0;
+// The ring of operands in shared memory on (1) or off (0): for tests and measurements.
+extern "C" void locus_delta_scan_set_ring(int on) { g_dr_ring = on; }
 
 extern "C" int locus_delta_scan(const float* q, int ldq, int off_q, const float* k, int ldk, int off_k, const float* v, int ldv,
                                 int off_v, const float* beta, const float* decay, float* state, long long slot_stride,
@@ -138,12 +220,19 @@ extern "C" int locus_delta_scan(const float* q, int ldq, int off_q, const float*
     a.d = d; a.dv = dv;
     const int col_groups = (dv + DR_CW - 1) / DR_CW;
     const dim3 grid((H * col_groups + 3) / 4, n_seg);
-    const int rpl = (d + 31) / 32;
-#define DR_SCAN(R) locus_launch(delta_scan_kernel<R>, grid, dim3(128), 0, stream, a, col_groups)
-    if (rpl <= 1) DR_SCAN(1);
-    else if (rpl <= 2) DR_SCAN(2);
-    else if (rpl <= 4) DR_SCAN(4);
-    else DR_SCAN(8);
+    const bool vec = ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k)) & 15) == 0 &&
+                     ((ldq | off_q | ldk | off_k | d) & 3) == 0;
+    const bool ring = vec && g_dr_ring && (reinterpret_cast<uintptr_t>(v) & 15) == 0 && ((ldv | off_v | dv) & 3) == 0;
+#define DR_SCAN(R, NST)                                                                                               \
+    do {                                                                                                              \
+        if (ring) locus_launch(delta_scan_kernel<R, true, true, NST>, grid, dim3(128), 0, stream, a, col_groups);     \
+        else if (vec) locus_launch(delta_scan_kernel<R, true, false, 2>, grid, dim3(128), 0, stream, a, col_groups);  \
+        else locus_launch(delta_scan_kernel<R, false, false, 2>, grid, dim3(128), 0, stream, a, col_groups);          \
+    } while (0)
+    if (d <= 32) DR_SCAN(4, 8);
+    else if (d <= 64) DR_SCAN(8, 8);
+    else if (d <= 128) DR_SCAN(16, 8);
+    else DR_SCAN(32, 4);
 #undef DR_SCAN
     return locus_launch_status();
 }

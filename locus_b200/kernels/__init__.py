@@ -738,12 +738,14 @@ def attn_chunk_tc(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, *, seg
                   seg_qn: torch.Tensor, seg_ctx: torch.Tensor, block_table: torch.Tensor,
                   items: torch.Tensor, n_items: int, n_heads: int, n_kv_heads: int, head_dim: int,
                   page_tokens: int, window: int, scale: float, n_splits: int = 1,
-                  part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None) -> None:
+                  part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None,
+                  keep_first: int = 0, sink: bool = False) -> None:
     """Attention of portions of prompts with tcgen05 tensor cores (scores and sums in tensor memory):
     ``items`` as for :func:`attn_chunk_mma` (tiles of 64 queries; a block takes an even one and the 64 queries
     behind it).  ``n_splits`` > 1 (:func:`attn_chunk_tc_splits`) with scratch of :func:`attn_chunk_tc_scratch`
     floats: the key tiles of every block are cut into that many ranges, merged in ascending order by a second
-    kernel."""
+    kernel.  ``keep_first`` (with a window): a request's first tokens stay in sight; ``sink``: one more term of score 0
+    in the softmax's denominator."""
     _cuda_c(q, "q")
     _cuda_c(out, "out")
     _cuda_c(pool, "pool")
@@ -761,7 +763,7 @@ def attn_chunk_tc(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, *, seg
         _p(q), LL(q.shape[0]), _p(pool), LL(pool.shape[0]), _p(out), _p(seg_q0), _p(seg_qn), _p(seg_ctx),
         _p(block_table), I(block_table.shape[1]), _p(items), I(n_items), I(n_heads), I(n_kv_heads), I(head_dim),
         I(page_tokens), I(window), F(scale), I(n_splits), _p(part_o if n_splits > 1 else None),
-        _p(part_ml if n_splits > 1 else None), _stream()
+        _p(part_ml if n_splits > 1 else None), I(keep_first if window > 0 else 0), I(1 if sink else 0), _stream()
     )
     if n_splits > 1 and code == 0:
         _count_launches(1)
@@ -833,8 +835,10 @@ def decode_units(max_items: int, n_heads: int, head_dim: int, dtype: torch.dtype
     except Exception:  # no GPU (host tests with emulated kernels)
         n_sm = 148
     streaming = max_items * n_heads + 8 * 16 * n_sm
-    if fixed_ranges:   # a window that keeps first tokens: the split kernel
-        return max(streaming, max_items * n_heads * max_splits)
+    if fixed_ranges:   # a window that keeps first tokens: one more range per (request, head), or the split kernel
+        if decode_streams(head_dim, dtype, page_tokens, max_items):
+            return streaming + max_items * n_heads
+        return max(streaming + max_items * n_heads, max_items * n_heads * max_splits)
     if decode_streams(head_dim, dtype, page_tokens, max_items):
         return streaming
     if n_kv_heads > 0 and attn_decode_gqa_takes(dtype, n_heads, n_kv_heads, head_dim, page_tokens,
@@ -866,8 +870,9 @@ def attn_decode(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, *, seg_q
                 part_ml: torch.Tensor, counters: torch.Tensor, max_splits: int, keep_first: int = 0,
                 sink: bool = False) -> None:
     """Attention of single new tokens: ``items`` [n_items] = segments with one new token.  ``keep_first``, ``sink``
-    as for :func:`attn_chunk` (such a step runs on the per-head kernels; with kept tokens on the one whose ranges are
-    fixed, which wants scratch for ``max_splits`` ranges per request and head).
+    as for :func:`attn_chunk` (the streaming kernels, per head and per group of query heads, walk the kept tokens in front
+    of the window as one more range of the request and want scratch for two ranges per request and head, the kernel whose
+    ranges are fixed for ``max_splits``: :func:`decode_units` with ``fixed_ranges``).
 
     ``part_o`` (float32, units * head_dim) and ``part_ml`` (float32, 2 * units) are scratch for
     partial results, ``units`` as :func:`decode_units` gives it (at least n_items * n_heads);
@@ -886,13 +891,14 @@ def attn_decode(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, *, seg_q
     _need(pool.numel() * pool.element_size() < (64 << 30), "attn_decode: a layer's cache pool of 64 GiB or more")
     _i32(counters, "counters")
     _need(counters.numel() >= n_items * n_heads, "attn_decode: counters too small")
-    if not (keep_first or sink) and attn_decode_gqa_takes(q.dtype, n_heads, n_kv_heads, head_dim, page_tokens, n_items):
+    if attn_decode_gqa_takes(q.dtype, n_heads, n_kv_heads, head_dim, page_tokens, n_items):
         # several query heads per key/value head: the kernel that reads every cache row once for its whole group
         code = _lib("attention_gqa").locus_attn_decode_gqa(
             _p(q), _p(pool), _p(out), _p(seg_q0), _p(seg_ctx), _p(block_table), I(block_table.shape[1]), _p(items),
             I(n_items), I(n_heads), I(n_kv_heads), I(head_dim), I(page_tokens), I(window), F(scale), _p(part_o),
             _p(part_ml), _p(counters), ctypes.c_longlong(max_units), I(GQA_COST_RANGE),
-            I(GQA_COST_MERGE_PER_HEAD * (n_heads // n_kv_heads)), _stream()
+            I(GQA_COST_MERGE_PER_HEAD * (n_heads // n_kv_heads)), I(keep_first if window > 0 else 0), I(1 if sink else 0),
+            _stream()
         )
         _check(code, "attn_decode", f"(grouped queries; heads {n_heads}/{n_kv_heads}, head_dim {head_dim})")
         return
@@ -1760,6 +1766,13 @@ def delta_rule(q: torch.Tensor, off_q: int, k: torch.Tensor, off_k: int, v: torc
         _p(decay), ctypes.c_void_p(state.data_ptr() + 4 * state_offset), LL(state.stride(0)), _p(state_slots), _p(seg_q0),
         _p(seg_qn), I(n_seg), _p(out), I(out.stride(0)), I(n_heads), I(heads_per_group), I(dim), I(v_dim), _stream())
     _check(code, "delta_scan", f"(heads {n_heads}, dim {dim}, v_dim {v_dim})")
+
+
+def delta_rule_variant(ring: Optional[bool]) -> None:
+    """The walk's ring of operands in shared memory (asynchronous copies several tokens ahead, where every operand lies on
+    16-byte boundaries) on (True) or off (False or None, the library's choice: one token fetched ahead into registers).
+    The arithmetic is the same either way.  For tests and measurements."""
+    _lib("delta_rule").locus_delta_scan_set_ring(I(1 if ring else 0))
 
 
 def delta_out(o: torch.Tensor, proj: torch.Tensor, off_g: int, w: torch.Tensor, eps: float, out: torch.Tensor, *,

@@ -252,8 +252,7 @@ class Attention(Mixer):
     def kernel_modules(self, dtype):
         special = bool(self.keep_first or self.sink)   # such an attention runs on the kernels that know of both
         return (["elementwise", "gemm_simt", "gemv", "attention"] + (["short_conv"] if self.shaped else [])
-                + (["gemm_skinny", "gemm_tc", "attention_mma"] if dtype == torch.bfloat16 else [])
-                + (["attention_tc", "attention_gqa"] if dtype == torch.bfloat16 and not special else []))
+                + (["gemm_skinny", "gemm_tc", "attention_mma", "attention_tc", "attention_gqa"] if dtype == torch.bfloat16 else []))
 
     def cache_needs(self):
         state = None
@@ -335,8 +334,8 @@ class Attention(Mixer):
             # few query tiles behind a long context: the keys of every tile are cut into ranges
             keys = max_splits * K.DECODE_SPLIT
             if self.window > 0:
-                keys = min(keys, self.window + K.TC_ATTN_QUERY_BLOCK)
-            if not special and K.attn_chunk_tc_takes(q, self.head_dim, gb.page_tokens, T, keys):
+                keys = min(keys, self.window + self.keep_first + K.TC_ATTN_QUERY_BLOCK)
+            if K.attn_chunk_tc_takes(q, self.head_dim, gb.page_tokens, T, keys):
                 n_splits = K.attn_chunk_tc_splits(tiles["n_chunk_items64"], self.n_heads, keys)
                 part_o = part_ml = None
                 if n_splits > 1:
@@ -344,7 +343,7 @@ class Attention(Mixer):
                     part_o = rt.buf("attention.chunk_tc_part_o", (n_o,), torch.float32)
                     part_ml = rt.buf("attention.chunk_tc_part_ml", (n_ml,), torch.float32)
                 K.attn_chunk_tc(q, cache.pool, o, items=tiles["chunk_items64"], n_items=tiles["n_chunk_items64"],
-                                n_splits=n_splits, part_o=part_o, part_ml=part_ml, **common)
+                                n_splits=n_splits, part_o=part_o, part_ml=part_ml, **extra, **common)
             elif K.attn_chunk_mma_takes(q, self.head_dim):
                 n_splits = K.attn_chunk_mma_splits(tiles["n_chunk_items64"], self.n_heads, keys)
                 part_o = part_ml = None

@@ -142,6 +142,8 @@ def _paged(args, B: int, ctx: int, new: int):
     i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
     meta = dict(seg_q0=i32([i * new for i in range(B)]), seg_qn=i32([new] * B), seg_ctx=i32([ctx] * B), block_table=table)
     kw = dict(n_heads=nh, n_kv_heads=nkv, head_dim=hd, page_tokens=P, window=args.window, scale=1 / math.sqrt(hd))
+    if args.keep_first or args.sink:
+        kw.update(keep_first=args.keep_first, sink=args.sink)
     return pool, q, torch.empty_like(q), meta, kw, i32
 
 
@@ -159,8 +161,10 @@ def bench_attn_decode(args) -> None:
                       **meta, **kw)
 
     us = _time(fn, args.iters, args.graph)
-    byts = B * (ctx + 1) * 2 * args.kv_heads * args.head_dim * pool.element_size()
-    print(f"attn_decode batch={B} ctx={ctx} heads={args.heads}/{args.kv_heads} head_dim={args.head_dim} {args.dtype}: "
+    seen = ctx + 1 if not args.window else min(ctx + 1, args.window + args.keep_first)   # the keys a new token sees
+    byts = B * seen * 2 * args.kv_heads * args.head_dim * pool.element_size()
+    print(f"attn_decode batch={B} ctx={ctx} heads={args.heads}/{args.kv_heads} head_dim={args.head_dim} window={args.window} "
+          f"keep_first={args.keep_first} sink={args.sink} {args.dtype}: "
           f"{us:.1f} us/call  cache read {byts / us / 1e3:.1f} GB/s")
 
 
@@ -192,7 +196,8 @@ def bench_attn_chunk(args) -> None:
 
     us = _time(fn, args.iters, args.graph)
     flops = 4.0 * args.heads * args.head_dim * (T * ctx + T * (T + 1) / 2)
-    print(f"attn_chunk tokens={T} ctx={ctx} heads={args.heads}/{args.kv_heads} head_dim={args.head_dim} "
+    print(f"attn_chunk tokens={T} ctx={ctx} heads={args.heads}/{args.kv_heads} head_dim={args.head_dim} window={args.window} "
+          f"keep_first={args.keep_first} sink={args.sink} "
           f"{f'tcgen05, {n_splits} key ranges' if tc else (f'mma.sync, {n_splits} key ranges' if mma else 'cuda cores')}: {us:.1f} us/call  {flops / us / 1e6:.1f} TFLOP/s (causal flops)")
 
 
@@ -242,6 +247,8 @@ def bench_recurrence(args) -> None:
 def _bench_delta(args, B, n, H, d, dv, G, q0, qn, slots, g) -> None:
     """The gated delta rule at the same sizes: unit keys, steps in (0, 1), decays near 1.  FLOPs: S^T k, S^T q and the
     decayed rank-one update per token and head; bytes: the states read and written, the operands, the outputs."""
+    if getattr(args, "ring", False):
+        K.delta_rule_variant(True)
     dev, T, Gn = "cuda:0", B * n, H // G
     q = (torch.randn(T, Gn * d, generator=g) * d ** -0.5).to(dev)
     k = torch.nn.functional.normalize(torch.randn(T, Gn, d, generator=g), dim=-1).reshape(T, Gn * d).to(dev)
@@ -352,8 +359,13 @@ def main(argv=None) -> int:
     ap.add_argument("--ones", action="store_true", help="recurrence: one column more, whose v is 1")
     ap.add_argument("--retention", action="store_true", help="recurrence: the fixed-decay kernels instead")
     ap.add_argument("--delta", action="store_true", help="recurrence: the gated delta rule instead")
+    ap.add_argument("--ring", action="store_true", help="recurrence --delta: the ring of operands in shared memory instead "
+                                                        "of one token fetched ahead into registers")
     ap.add_argument("--page-tokens", type=int, default=64)
     ap.add_argument("--window", type=int, default=0)
+    ap.add_argument("--keep-first", type=int, default=0, dest="keep_first",
+                    help="attention: with --window, a request's first tokens stay in sight")
+    ap.add_argument("--sink", action="store_true", help="attention: one more term of score 0 in the softmax's denominator")
     ap.add_argument("--experts", type=int, default=60)
     ap.add_argument("--top-k", type=int, default=4)
     ap.add_argument("--tile", type=int, default=0, help="experts: rows of a tile instead of the engine's choice")

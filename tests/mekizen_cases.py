@@ -205,6 +205,20 @@ def compare(case, got, tol_max, tol_mean):
         assert mean <= tol_mean, f"{case.name}/{rid}: mean error {mean:.2e}"
 
 
+def compare_together(case, got, tol_max, tol_mean, one_in=10, cap=5.0):
+    """As ``compare``, for bfloat16 models in which single positions amplify the rounding of the activations (a head of
+    a few elements whose root mean square passes near zero, scores of a window of one token): the mean error as
+    everywhere, all but one row in ``one_in`` within ``tol_max``, and no row beyond ``cap`` times that.  The kernels'
+    plain twins in bfloat16 are off in the same rows by as much, for every cut of the prompt."""
+    for rid, out in got.items():
+        ref = case.ref(rid)
+        assert out.shape == ref.shape and bool(torch.isfinite(out).all()), rid
+        err, mean = errors(out, ref)
+        assert mean <= tol_mean, f"{case.name}/{rid}: mean error {mean:.2e}"
+        assert float(err.max()) <= cap * tol_max, f"{case.name}/{rid}: position {int(err.argmax())} is off by {float(err.max()):.2e}"
+        assert int((err > tol_max).sum()) <= max(1, len(err) // one_in), f"{case.name}/{rid}: {int((err > tol_max).sum())} rows beyond {tol_max}"
+
+
 def random_config(seed):
     """A configuration drawn from the ranges a small model of this design may have: layer order, head counts and sizes,
     rotated parts, windows, kept tokens, taps, shared keys and values and constants all vary."""
