@@ -17,17 +17,15 @@
 //                lane that kept rows l, l + 32, ... of all four columns needed forty-five: with many requests the
 //                shuffle unit, one warp instruction a cycle and SM, was the limit.  The four rows are one 16-byte load
 //                of k and of q where the operands allow it, and the 8 row groups read one 128-byte line.  The next
-//                token's operands are fetched while this one is worked on.  The order of every sum is fixed by d
-//                alone, so a cut of a prompt changes nothing at all.
-//                Where every operand allows 16-byte copies (RING) each warp keeps a ring of the next tokens' operands
-//                in shared memory, filled by asynchronous copies several tokens ahead: a token's sums and exchanges
-//                take a fraction of a load's way to L2 and back, and with four warps or fewer on an SM (one request,
-//                16 heads) one token fetched ahead left the walk waiting on memory most of the time.  The registers
-//                are then filled from the ring one token ahead as before; the arithmetic is the same.
+//                token's operands are fetched while this one is worked on: one token ahead, into registers.  (Measured
+//                at one request of 2,048 tokens, 16 heads of 128 x 128, where each scheduler has one warp: two or three
+//                tokens ahead, a ring of operands in shared memory filled by asynchronous copies or through registers,
+//                and one column to a warp with four times the warps were all slower, by a tenth to a factor of two:
+//                each adds instructions or loads in flight to a walk that issues one dependent instruction every six
+//                cycles.)  The order of every sum is fixed by d alone, so a cut of a prompt changes nothing at all.
 //   delta_out    a head's read-out divided by its root mean square, times a weight, times silu(gate).
 #include "common.cuh"
 
-#define DR_CW 4
 
 struct DeltaArgs {
     const float* q;
@@ -45,40 +43,26 @@ struct DeltaArgs {
     int H, heads_per_group, d, dv;
 };
 
+#define DR_CW 4   // columns of a warp
+#define DR_PF 1   // tokens whose operands are fetched ahead into registers
+
 // R: rows of a column that a lane keeps (d <= 8 R).  VEC: q's and k's rows of a head start on 16-byte boundaries and d
 // is a multiple of 4, so four rows are one load.
-// One stage of a warp's ring: q and k (8 R rows each), then v's four columns, beta and the decay.
-#define DR_STAGE(R) (16 * (R) + 8)
-
-__device__ __forceinline__ void dr_copy16(float* dst, const float* src) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(static_cast<unsigned>(__cvta_generic_to_shared(dst))), "l"(src)
-                 : "memory");
-}
-__device__ __forceinline__ void dr_copy4(float* dst, const float* src) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(static_cast<unsigned>(__cvta_generic_to_shared(dst))), "l"(src)
-                 : "memory");
-}
-__device__ __forceinline__ void dr_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void dr_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-
-// RING (implies VEC; v's four columns of a warp are one aligned 16-byte piece too): NST stages per warp.
-template <int R, bool VEC, bool RING, int NST>
+template <int R, bool VEC>
 __global__ void __launch_bounds__(128) delta_scan_kernel(const DeltaArgs a, int col_groups) {
     pdl_entry();
     pdl_trigger();
-    __shared__ __align__(16) float ring_all[RING ? 4 * NST * DR_STAGE(R) : 4];
-    float* const ring = ring_all + (RING ? (threadIdx.x >> 5) * NST * DR_STAGE(R) : 0);
-    const int lane = threadIdx.x & 31, lr = lane >> 2, lc = lane & 3;
+    constexpr int CW = DR_CW, PF = DR_PF, NG = 32 / CW;  // (NG groups of rows)
+    const int lane = threadIdx.x & 31, lr = lane / CW, lc = lane % CW;
     const int unit = blockIdx.x * 4 + (threadIdx.x >> 5);  // (head, column group)
     const int seg = blockIdx.y;
     if (unit >= a.H * col_groups) return;
     const int qn = a.seg_qn[seg];
-    const int h = unit / col_groups, col = (unit % col_groups) * DR_CW + lc;
+    const int h = unit / col_groups, col = (unit % col_groups) * CW + lc;
     const int d = a.d, dv = a.dv, q0 = a.seg_q0[seg];
     const bool col_ok = col < dv;
     float* S = a.state + static_cast<size_t>(a.state_slots[seg]) * a.slot_stride + static_cast<size_t>(h) * d * dv;
-    auto row_of = [&](int i) { return 32 * (i >> 2) + 4 * lr + (i & 3); };
+    auto row_of = [&](int i) { return 4 * NG * (i >> 2) + 4 * lr + (i & 3); };
     float s[R];
 #pragma unroll
     for (int i = 0; i < R; ++i) {
@@ -87,113 +71,75 @@ __global__ void __launch_bounds__(128) delta_scan_kernel(const DeltaArgs a, int 
     }
     const int g = h / a.heads_per_group;
     const int off_q = a.off_q + g * d, off_k = a.off_k + g * d, off_v = a.off_v + h * dv;
-    float qn_[R], kn_[R], vn_ = 0.f, beta_n = 0.f, decay_n = 0.f;
-    // token t's operands on their way into its stage of the ring; one group of copies per token, empty behind the last
-    auto stage_in = [&](int t) {
-        if (t < qn) {
-            float* st = ring + (t % NST) * DR_STAGE(R);
-            const size_t row = static_cast<size_t>(q0 + t);
-            const float* qp = a.q + row * a.ldq + off_q;
-            const float* kp = a.k + row * a.ldk + off_k;
-            for (int i = lane; 4 * i < d; i += 32) {
-                dr_copy16(st + 4 * i, qp + 4 * i);
-                dr_copy16(st + 8 * R + 4 * i, kp + 4 * i);
-            }
-            if (lane == 0) dr_copy16(st + 16 * R, a.v + row * a.ldv + off_v + (col - lc));
-            if (lane == 1) dr_copy4(st + 16 * R + 4, a.beta + row * a.H + h);
-            if (lane == 2) dr_copy4(st + 16 * R + 5, a.decay + row * a.H + h);
-        }
-        dr_commit();
-    };
-    auto fetch = [&](int t) {
-        if (RING) {
-            // the groups of tokens up to t + NST - 2 are committed: all but the newest NST - 2 have landed, so has
-            // token t's; the barrier makes the other lanes' copies visible and orders this read behind the reads of
-            // the stage that the next copy overwrites
-            dr_wait<NST - 2>();
-            __syncwarp();
-            const float* st = ring + (t % NST) * DR_STAGE(R);
-#pragma unroll
-            for (int j = 0; j < R / 4; ++j) {
-                const int r = 32 * j + 4 * lr;
-                float4 qv = make_float4(0.f, 0.f, 0.f, 0.f), kv = qv;
-                if (r < d) {
-                    qv = *reinterpret_cast<const float4*>(st + r);
-                    kv = *reinterpret_cast<const float4*>(st + 8 * R + r);
-                }
-                qn_[4 * j] = qv.x; qn_[4 * j + 1] = qv.y; qn_[4 * j + 2] = qv.z; qn_[4 * j + 3] = qv.w;
-                kn_[4 * j] = kv.x; kn_[4 * j + 1] = kv.y; kn_[4 * j + 2] = kv.z; kn_[4 * j + 3] = kv.w;
-            }
-            vn_ = st[16 * R + lc];
-            beta_n = st[16 * R + 4];
-            decay_n = st[16 * R + 5];
-            return;
-        }
+    float qn_[PF][R], kn_[PF][R], vn_[PF], beta_n[PF], decay_n[PF];
+    auto fetch = [&](int t, int j) {  // token t's operands into register set j
+        if (t >= qn) return;
         const size_t row = static_cast<size_t>(q0 + t);
         const float* qp = a.q + row * a.ldq + off_q;
         const float* kp = a.k + row * a.ldk + off_k;
         if (VEC) {
 #pragma unroll
-            for (int j = 0; j < R / 4; ++j) {
-                const int r = 32 * j + 4 * lr;
+            for (int b = 0; b < R / 4; ++b) {
+                const int r = 4 * NG * b + 4 * lr;
                 float4 qv = make_float4(0.f, 0.f, 0.f, 0.f), kv = qv;
                 if (r < d) {
                     qv = *reinterpret_cast<const float4*>(qp + r);
                     kv = *reinterpret_cast<const float4*>(kp + r);
                 }
-                qn_[4 * j] = qv.x; qn_[4 * j + 1] = qv.y; qn_[4 * j + 2] = qv.z; qn_[4 * j + 3] = qv.w;
-                kn_[4 * j] = kv.x; kn_[4 * j + 1] = kv.y; kn_[4 * j + 2] = kv.z; kn_[4 * j + 3] = kv.w;
+                qn_[j][4 * b] = qv.x; qn_[j][4 * b + 1] = qv.y; qn_[j][4 * b + 2] = qv.z; qn_[j][4 * b + 3] = qv.w;
+                kn_[j][4 * b] = kv.x; kn_[j][4 * b + 1] = kv.y; kn_[j][4 * b + 2] = kv.z; kn_[j][4 * b + 3] = kv.w;
             }
         } else {
 #pragma unroll
             for (int i = 0; i < R; ++i) {
                 const int r = row_of(i);
-                qn_[i] = r < d ? qp[r] : 0.f;
-                kn_[i] = r < d ? kp[r] : 0.f;
+                qn_[j][i] = r < d ? qp[r] : 0.f;
+                kn_[j][i] = r < d ? kp[r] : 0.f;
             }
         }
-        vn_ = col_ok ? a.v[row * a.ldv + off_v + col] : 0.f;
-        beta_n = a.beta[row * a.H + h];
-        decay_n = a.decay[row * a.H + h];
+        vn_[j] = col_ok ? a.v[row * a.ldv + off_v + col] : 0.f;
+        beta_n[j] = a.beta[row * a.H + h];
+        decay_n[j] = a.decay[row * a.H + h];
     };
-    if (RING) {
-#pragma unroll 1
-        for (int t = 0; t < NST - 1; ++t) stage_in(t);
-    }
-    if (qn > 0) fetch(0);
-    for (int t = 0; t < qn; ++t) {
-        float qq[R], kk[R];
-        const float beta = beta_n, gd = decay_n, vv = vn_;
 #pragma unroll
-        for (int i = 0; i < R; ++i) {
-            qq[i] = qn_[i];
-            kk[i] = kn_[i];
+    for (int j = 0; j < PF; ++j) fetch(j, j);
+    for (int t0 = 0; t0 < qn; t0 += PF) {
+#pragma unroll
+        for (int j = 0; j < PF; ++j) {
+            const int t = t0 + j;
+            if (t >= qn) break;
+            float qq[R], kk[R];
+            const float beta = beta_n[j], gd = decay_n[j], vv = vn_[j];
+#pragma unroll
+            for (int i = 0; i < R; ++i) {
+                qq[i] = qn_[j][i];
+                kk[i] = kn_[j][i];
+            }
+            fetch(t + PF, j);  // a later token's operands are on their way while this one is worked on
+            // two partial sums each: a chain of R dependent additions is as long as the exchanges behind it
+            float sk0 = 0.f, sk1 = 0.f, sq0 = 0.f, sq1 = 0.f, kq0 = 0.f, kq1 = 0.f;
+#pragma unroll
+            for (int i = 0; i < R; i += 2) {
+                sk0 = fmaf(s[i], kk[i], sk0);
+                sq0 = fmaf(s[i], qq[i], sq0);
+                kq0 = fmaf(kk[i], qq[i], kq0);
+                sk1 = fmaf(s[i + 1], kk[i + 1], sk1);
+                sq1 = fmaf(s[i + 1], qq[i + 1], sq1);
+                kq1 = fmaf(kk[i + 1], qq[i + 1], kq1);
+            }
+            float sk = sk0 + sk1, sq = sq0 + sq1, kq = kq0 + kq1;
+#pragma unroll
+            for (int m = CW; m < 32; m <<= 1) {  // across the row groups of this column
+                sk += __shfl_xor_sync(0xffffffffu, sk, m);
+                sq += __shfl_xor_sync(0xffffffffu, sq, m);
+                kq += __shfl_xor_sync(0xffffffffu, kq, m);
+            }
+            const float u = beta * (vv - gd * sk);
+            const float o = fmaf(u, kq, gd * sq);
+#pragma unroll
+            for (int i = 0; i < R; ++i) s[i] = fmaf(gd, s[i], kk[i] * u);
+            if (lr == 0 && col_ok) a.out[static_cast<size_t>(q0 + t) * a.ldo + h * dv + col] = o;
         }
-        if (RING) stage_in(t + NST - 1);  // into the stage that token t - 1 left (read one iteration ago, a barrier since)
-        if (t + 1 < qn) fetch(t + 1);  // the next token's operands are on their way while this one is worked on
-        // two partial sums each: a chain of R dependent additions is as long as the exchanges behind it
-        float sk0 = 0.f, sk1 = 0.f, sq0 = 0.f, sq1 = 0.f, kq0 = 0.f, kq1 = 0.f;
-#pragma unroll
-        for (int i = 0; i < R; i += 2) {
-            sk0 = fmaf(s[i], kk[i], sk0);
-            sq0 = fmaf(s[i], qq[i], sq0);
-            kq0 = fmaf(kk[i], qq[i], kq0);
-            sk1 = fmaf(s[i + 1], kk[i + 1], sk1);
-            sq1 = fmaf(s[i + 1], qq[i + 1], sq1);
-            kq1 = fmaf(kk[i + 1], qq[i + 1], kq1);
-        }
-        float sk = sk0 + sk1, sq = sq0 + sq1, kq = kq0 + kq1;
-#pragma unroll
-        for (int m = 4; m < 32; m <<= 1) {  // across the 8 row groups of this column
-            sk += __shfl_xor_sync(0xffffffffu, sk, m);
-            sq += __shfl_xor_sync(0xffffffffu, sq, m);
-            kq += __shfl_xor_sync(0xffffffffu, kq, m);
-        }
-        const float u = beta * (vv - gd * sk);
-        const float o = fmaf(u, kq, gd * sq);
-#pragma unroll
-        for (int i = 0; i < R; ++i) s[i] = fmaf(gd, s[i], kk[i] * u);
-        if (lr == 0 && col_ok) a.out[static_cast<size_t>(q0 + t) * a.ldo + h * dv + col] = o;
     }
 #pragma unroll
     for (int i = 0; i < R; ++i) {
@@ -201,10 +147,6 @@ __global__ void __launch_bounds__(128) delta_scan_kernel(const DeltaArgs a, int 
         if (r < d && col_ok) S[static_cast<size_t>(r) * dv + col] = s[i];
     }
 }
-
-static int g_dr_ring = 0;
-// The ring of operands in shared memory on (1) or off (0): for tests and measurements.
-extern "C" void locus_delta_scan_set_ring(int on) { g_dr_ring = on; }
 
 extern "C" int locus_delta_scan(const float* q, int ldq, int off_q, const float* k, int ldk, int off_k, const float* v, int ldv,
                                 int off_v, const float* beta, const float* decay, float* state, long long slot_stride,
@@ -218,21 +160,19 @@ extern "C" int locus_delta_scan(const float* q, int ldq, int off_q, const float*
     a.seg_q0 = seg_q0; a.seg_qn = seg_qn; a.out = out; a.slot_stride = slot_stride; a.ldq = ldq; a.off_q = off_q;
     a.ldk = ldk; a.off_k = off_k; a.ldv = ldv; a.off_v = off_v; a.ldo = ldo; a.H = H; a.heads_per_group = heads_per_group;
     a.d = d; a.dv = dv;
-    const int col_groups = (dv + DR_CW - 1) / DR_CW;
-    const dim3 grid((H * col_groups + 3) / 4, n_seg);
     const bool vec = ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k)) & 15) == 0 &&
                      ((ldq | off_q | ldk | off_k | d) & 3) == 0;
-    const bool ring = vec && g_dr_ring && (reinterpret_cast<uintptr_t>(v) & 15) == 0 && ((ldv | off_v | dv) & 3) == 0;
-#define DR_SCAN(R, NST)                                                                                               \
-    do {                                                                                                              \
-        if (ring) locus_launch(delta_scan_kernel<R, true, true, NST>, grid, dim3(128), 0, stream, a, col_groups);     \
-        else if (vec) locus_launch(delta_scan_kernel<R, true, false, 2>, grid, dim3(128), 0, stream, a, col_groups);  \
-        else locus_launch(delta_scan_kernel<R, false, false, 2>, grid, dim3(128), 0, stream, a, col_groups);          \
+    const int col_groups = (dv + DR_CW - 1) / DR_CW;
+    const dim3 grid((H * col_groups + 3) / 4, n_seg);
+#define DR_SCAN(R)                                                                              \
+    do {                                                                                        \
+        if (vec) locus_launch(delta_scan_kernel<R, true>, grid, dim3(128), 0, stream, a, col_groups);  \
+        else locus_launch(delta_scan_kernel<R, false>, grid, dim3(128), 0, stream, a, col_groups);     \
     } while (0)
-    if (d <= 32) DR_SCAN(4, 8);
-    else if (d <= 64) DR_SCAN(8, 8);
-    else if (d <= 128) DR_SCAN(16, 8);
-    else DR_SCAN(32, 4);
+    if (d <= 32) DR_SCAN(4);
+    else if (d <= 64) DR_SCAN(8);
+    else if (d <= 128) DR_SCAN(16);
+    else DR_SCAN(32);
 #undef DR_SCAN
     return locus_launch_status();
 }

@@ -1768,13 +1768,6 @@ def delta_rule(q: torch.Tensor, off_q: int, k: torch.Tensor, off_k: int, v: torc
     _check(code, "delta_scan", f"(heads {n_heads}, dim {dim}, v_dim {v_dim})")
 
 
-def delta_rule_variant(ring: Optional[bool]) -> None:
-    """The walk's ring of operands in shared memory (asynchronous copies several tokens ahead, where every operand lies on
-    16-byte boundaries) on (True) or off (False or None, the library's choice: one token fetched ahead into registers).
-    The arithmetic is the same either way.  For tests and measurements."""
-    _lib("delta_rule").locus_delta_scan_set_ring(I(1 if ring else 0))
-
-
 def delta_out(o: torch.Tensor, proj: torch.Tensor, off_g: int, w: torch.Tensor, eps: float, out: torch.Tensor, *,
               n_heads: int, v_dim: int) -> None:
     """out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * w * silu(gate[t, h, :]); the gate: the columns of

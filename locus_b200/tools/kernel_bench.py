@@ -247,8 +247,6 @@ def bench_recurrence(args) -> None:
 def _bench_delta(args, B, n, H, d, dv, G, q0, qn, slots, g) -> None:
     """The gated delta rule at the same sizes: unit keys, steps in (0, 1), decays near 1.  FLOPs: S^T k, S^T q and the
     decayed rank-one update per token and head; bytes: the states read and written, the operands, the outputs."""
-    if getattr(args, "ring", False):
-        K.delta_rule_variant(True)
     dev, T, Gn = "cuda:0", B * n, H // G
     q = (torch.randn(T, Gn * d, generator=g) * d ** -0.5).to(dev)
     k = torch.nn.functional.normalize(torch.randn(T, Gn, d, generator=g), dim=-1).reshape(T, Gn * d).to(dev)
@@ -359,8 +357,6 @@ def main(argv=None) -> int:
     ap.add_argument("--ones", action="store_true", help="recurrence: one column more, whose v is 1")
     ap.add_argument("--retention", action="store_true", help="recurrence: the fixed-decay kernels instead")
     ap.add_argument("--delta", action="store_true", help="recurrence: the gated delta rule instead")
-    ap.add_argument("--ring", action="store_true", help="recurrence --delta: the ring of operands in shared memory instead "
-                                                        "of one token fetched ahead into registers")
     ap.add_argument("--page-tokens", type=int, default=64)
     ap.add_argument("--window", type=int, default=0)
     ap.add_argument("--keep-first", type=int, default=0, dest="keep_first",
