@@ -3,3 +3,4 @@ from .base import (ArchEntry, ConfigError, arch_name_of, archs, find_arch, load_
 from .qwen2_moe import Qwen2MoeConfig  # noqa: F401
 from .lalepel import LalepelConfig  # noqa: F401
 from .pozozen import PozozenConfig  # noqa: F401
+from .gugozen import GugozenConfig  # noqa: F401

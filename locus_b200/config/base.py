@@ -34,6 +34,15 @@ class ArchEntry:
     description: str
     parse_config: Callable[[Dict[str, Any]], Any]
     build_plan: Callable[[Any], Any]
+    # True: a size of this architecture is given by a stored tensor's shape alone, and ``build_plan`` also takes
+    # ``tensor_shapes`` (name -> shape of the model folder's tensors) when a folder is at hand
+    sizes_from_tensors: bool = False
+
+    def plan(self, cfg, source=None):
+        """The plan of ``cfg``; ``source``: the model folder's tensors (``names()``, ``info(name)``), if there is one."""
+        if self.sizes_from_tensors and source is not None:
+            return self.build_plan(cfg, tensor_shapes={n: tuple(source.info(n)[1]) for n in source.names()})
+        return self.build_plan(cfg)
 
 
 _ARCHS: Dict[str, ArchEntry] = {}

@@ -15,6 +15,7 @@
 // Cache layout of one layer: [n_pages][2 (K, V)][nkv][page_tokens][hd].
 #include "common.cuh"
 #include "attn_ranges.cuh"
+#include "sink.cuh"
 
 struct AttnArgs {
     const void* q;            // [T, nh * hd]
@@ -29,6 +30,7 @@ struct AttnArgs {
                               // decode: [n_items] segment ids
     int nh, nkv, hd, page_tokens, window;
     int keep_first, sink;     // see the head of the file
+    const float* sink_val;    // with sink: a learned score per query head in its place (null: the score 0)
     float scale;
     // decode only
     float* part_o;            // [n_items, nh, max_splits, hd]
@@ -179,7 +181,7 @@ __global__ void __launch_bounds__(128) attn_chunk_kernel(AttnArgs a) {
         __syncthreads();
     }
     if (my_q < nq) {
-        const float inv = 1.0f / (a.sink ? l_s[my_q] + expf(-m_s[my_q]) : l_s[my_q]);
+        const float inv = 1.0f / (a.sink ? l_s[my_q] + sink_term(a.sink_val, h, m_s[my_q]) : l_s[my_q]);
         T* o = static_cast<T*>(a.out) + (static_cast<size_t>(row0 + my_q) * a.nh + h) * hd;
 #pragma unroll
         for (int dd = 0; dd < 32; ++dd) {
@@ -391,7 +393,7 @@ __global__ void __launch_bounds__(128) attn_decode_split_kernel(AttnArgs a) {
     if (tid == 0) {
         float L = 0.f;
         for (int i = 0; i < ns; ++i) L += __ldcg(a.part_ml + 2 * (base + LIVE_SPLIT(i)) + 1) * wsplit[i];
-        if (a.sink) L += expf(-M);
+        if (a.sink) L += sink_term(a.sink_val, h, M);
         inv_sh = 1.0f / L;
     }
     __syncthreads();
@@ -743,7 +745,7 @@ __global__ void __launch_bounds__(32 * DS_WARPS, DEEP ? 2 : 4) attn_decode_strea
                 o.z = fmaf(v.z, w, o.z);
                 o.w = fmaf(v.w, w, o.w);
             }
-            if (a.sink) L += exp2f(-M);   // scores are in base 2 here
+            if (a.sink) L += sink_term2(a.sink_val, h, M);   // scores are in base 2 here
             const float inv = 1.0f / L;
             T* dst = static_cast<T*>(a.out) + (static_cast<size_t>(row) * a.nh + h) * hd + d;
             dst[0] = from_f<T>(o.x * inv);
@@ -780,12 +782,13 @@ static int check_common(int nh, int nkv, int hd, int page_tokens, int window, in
 static AttnArgs make_args(const void* q, const void* pool, void* out, const int* seg_q0,
                           const int* seg_qn, const int* seg_ctx, const int* block_table,
                           int table_stride, const int* items, int nh, int nkv, int hd,
-                          int page_tokens, int window, float scale, int keep_first = 0, int sink = 0) {
+                          int page_tokens, int window, float scale, int keep_first = 0, int sink = 0,
+                          const float* sink_val = nullptr) {
     AttnArgs a;
     a.q = q; a.pool = pool; a.out = out; a.seg_q0 = seg_q0; a.seg_qn = seg_qn; a.seg_ctx = seg_ctx;
     a.block_table = block_table; a.table_stride = table_stride; a.items = items; a.nh = nh;
     a.nkv = nkv; a.hd = hd; a.page_tokens = page_tokens; a.window = window; a.scale = scale;
-    a.keep_first = window > 0 ? keep_first : 0; a.sink = sink;
+    a.keep_first = window > 0 ? keep_first : 0; a.sink = sink; a.sink_val = sink ? sink_val : nullptr;
     a.part_o = nullptr; a.part_ml = nullptr; a.counters = nullptr; a.max_splits = 0;
     return a;
 }
@@ -794,12 +797,12 @@ extern "C" int locus_attn_chunk(const void* q, int dt, const void* pool, void* o
                                 const int* seg_q0, const int* seg_qn, const int* seg_ctx,
                                 const int* block_table, int table_stride, const int* items,
                                 int n_items, int nh, int nkv, int hd, int page_tokens, int window,
-                                float scale, int keep_first, int sink, cudaStream_t stream) {
+                                float scale, int keep_first, int sink, const float* sink_val, cudaStream_t stream) {
     if (n_items <= 0) return 0;
     if (int e = check_common(nh, nkv, hd, page_tokens, window, keep_first)) return e;
     if (n_items > 65535) return LOCUS_ERR_UNSUPPORTED;
     AttnArgs a = make_args(q, pool, out, seg_q0, seg_qn, seg_ctx, block_table, table_stride, items,
-                           nh, nkv, hd, page_tokens, window, scale, keep_first, sink);
+                           nh, nkv, hd, page_tokens, window, scale, keep_first, sink, sink_val);
     const size_t smem = sizeof(float) * (CHUNK_BQ * hd + CHUNK_TK * (hd + 1) + CHUNK_TK * hd +
                                          CHUNK_BQ * (CHUNK_TK + 1) + 3 * CHUNK_BQ);
     dim3 grid(nh, n_items);
@@ -825,12 +828,13 @@ extern "C" int locus_attn_decode(const void* q, int dt, const void* pool, void* 
                                  const int* block_table, int table_stride, const int* items,
                                  int n_items, int nh, int nkv, int hd, int page_tokens, int window,
                                  float scale, float* part_o, float* part_ml, int* counters, int max_splits,
-                                 long long max_units, int keep_first, int sink, cudaStream_t stream) {
+                                 long long max_units, int keep_first, int sink, const float* sink_val,
+                                 cudaStream_t stream) {
     if (n_items <= 0) return 0;
     if (int e = check_common(nh, nkv, hd, page_tokens, window, keep_first)) return e;
     if (nh > 65535 || max_splits <= 0 || max_splits > 65535) return LOCUS_ERR_UNSUPPORTED;
     AttnArgs a = make_args(q, pool, out, seg_q0, seg_qn, seg_ctx, block_table, table_stride, items,
-                           nh, nkv, hd, page_tokens, window, scale, keep_first, sink);
+                           nh, nkv, hd, page_tokens, window, scale, keep_first, sink, sink_val);
     a.part_o = part_o; a.part_ml = part_ml; a.counters = counters; a.max_splits = max_splits;
     if (counters == nullptr) return LOCUS_ERR_UNSUPPORTED;
     // (one partial result per request and head at least; two where kept first tokens are a range of their own)
@@ -945,5 +949,5 @@ extern "C" int locus_attn_decode_static(const void* q, int dt, const void* pool,
     // and the counters are zero between calls.
     return locus_attn_decode(q, dt, pool, out, seg_q0, seg_qn, seg_ctx, block_table, table_stride,
                              items, n_items, nh, nkv, hd, page_tokens, window, scale, part_o, part_ml,
-                             g_attn_static_cnt_ptr[dev], max_splits, cap, 0, 0, stream);
+                             g_attn_static_cnt_ptr[dev], max_splits, cap, 0, 0, nullptr, stream);
 }

@@ -31,6 +31,7 @@
 // Takes bfloat16, head sizes 64 and 128, groups of 2 to 16 query heads, pages of a multiple of 16 tokens.
 #include "common.cuh"
 #include "attn_ranges.cuh"
+#include "sink.cuh"
 
 struct GqaArgs {
     const bf16* q;            // [T, nh * hd]
@@ -42,6 +43,7 @@ struct GqaArgs {
     int table_stride;
     const int* items;         // [n_items] segments with one new token
     int nh, nkv, page_tokens, window;
+    const float* sink_val;    // with sink: a learned score per query head in its place (null: the score 0)
     int keep_first, sink;     // with a window: a request's first tokens stay in sight; one more term of score 0 in the denominator
     float scale;
     float* part_o;            // [units * G][hd]
@@ -423,7 +425,9 @@ __global__ void __launch_bounds__(32 * GQW, 1) attn_decode_gqa_kernel(GqaArgs a,
                     acc1.z = fmaf(v1.z, w1, acc1.z); acc1.w = fmaf(v1.w, w1, acc1.w);
                 }
                 // (the sink: one more term of score 0; scores are in base 2 here)
-                const float inv0 = 1.0f / (a.sink ? L0 + exp2f(-M0) : L0), inv1 = 1.0f / (a.sink ? L1 + exp2f(-M1) : L1);
+                const int h0 = kvh * G + g, h1 = h0 + (two ? 1 : 0);
+                const float inv0 = 1.0f / (a.sink ? L0 + sink_term2(a.sink_val, h0, M0) : L0);
+                const float inv1 = 1.0f / (a.sink ? L1 + sink_term2(a.sink_val, h1, M1) : L1);
                 bf16* dst = a.out + (static_cast<size_t>(row) * a.nh + static_cast<size_t>(kvh) * G + g) * HD + d;
                 dst[0] = from_f<bf16>(acc0.x * inv0);
                 dst[1] = from_f<bf16>(acc0.y * inv0);
@@ -459,7 +463,8 @@ extern "C" int locus_attn_decode_gqa(const void* q, const void* pool, void* out,
                                      const int* block_table, int table_stride, const int* items, int n_items, int nh,
                                      int nkv, int hd, int page_tokens, int window, float scale, float* part_o,
                                      float* part_ml, int* counters, long long max_units, int cost_range,
-                                     int cost_merge, int keep_first, int sink, cudaStream_t stream) {
+                                     int cost_merge, int keep_first, int sink, const float* sink_val,
+                                     cudaStream_t stream) {
     if (n_items <= 0) return 0;
     if (!locus_attn_decode_gqa_takes(LOCUS_DT_BF16, nh, nkv, hd, page_tokens, n_items) || window < 0 || counters == nullptr)
         return LOCUS_ERR_UNSUPPORTED;
@@ -482,7 +487,7 @@ extern "C" int locus_attn_decode_gqa(const void* q, const void* pool, void* out,
     a.out = static_cast<bf16*>(out);
     a.seg_q0 = seg_q0; a.seg_ctx = seg_ctx; a.block_table = block_table; a.table_stride = table_stride; a.items = items;
     a.nh = nh; a.nkv = nkv; a.page_tokens = page_tokens; a.window = window; a.scale = scale;
-    a.keep_first = keep_first; a.sink = sink;
+    a.keep_first = keep_first; a.sink = sink; a.sink_val = sink ? sink_val : nullptr;
     a.part_o = part_o; a.part_ml = part_ml; a.counters = counters;
     const dim3 grid(n_sm);
     const bool wide = nh / nkv > 8;

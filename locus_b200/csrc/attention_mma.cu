@@ -20,6 +20,7 @@
 // caller uses the CUDA-core kernel.  Rows in shared memory are
 // padded by 16 bytes so that ldmatrix reads no bank twice.
 #include "common.cuh"
+#include "sink.cuh"
 
 #define MQ 64    // queries per block
 #define MK 64    // keys per tile
@@ -35,6 +36,7 @@ struct MmaAttnArgs {
     int table_stride;
     const int* items;
     int nh, nkv, page_tokens, window;
+    const float* sink_val;  // with sink: a learned score per query head in its place (null: the score 0)
     int keep_first, sink;   // a window that keeps a request's first tokens in sight; one more term of score 0 in the denominator
     float scale;
     int n_splits;     // ranges of key tiles per item (1: the block writes out itself)
@@ -312,7 +314,7 @@ __global__ void __launch_bounds__(128) attn_chunk_mma_kernel(MmaAttnArgs a) {
     for (int rr = 0; rr < 2; ++rr) {
         const int r = warp * 16 + g + rr * 8;
         if (r >= nq) continue;
-        const float inv = 1.0f / (a.sink ? l_run[rr] + exp2f(-m_run[rr]) : l_run[rr]);   // (scores are in base 2)
+        const float inv = 1.0f / (a.sink ? l_run[rr] + sink_term2(a.sink_val, h, m_run[rr]) : l_run[rr]);   // (scores are in base 2)
         bf16* dst = a.out + (static_cast<size_t>(row0 + r) * a.nh + h) * HD;
 #pragma unroll
         for (int d = 0; d < DT; ++d) {
@@ -361,7 +363,7 @@ __global__ void __launch_bounds__(128) attn_chunk_merge_kernel(MmaAttnArgs a, in
         x += v[s].x * w;
         y += v[s].y * w;
     }
-    if (a.sink) L += exp2f(-M);
+    if (a.sink) L += sink_term2(a.sink_val, h, M);
     const float inv = 1.0f / L;
     *reinterpret_cast<uint32_t*>(a.out + (static_cast<size_t>(row0 + r) * a.nh + h) * hd + d) = pack_bf16(x * inv, y * inv);
 }
@@ -388,7 +390,7 @@ static int launch(const MmaAttnArgs& a, int n_items, cudaStream_t stream) {
 extern "C" int locus_attn_chunk_mma(const void* q, const void* pool, void* out, const int* seg_q0, const int* seg_qn,
                                     const int* seg_ctx, const int* block_table, int table_stride, const int* items,
                                     int n_items, int nh, int nkv, int hd, int page_tokens, int window, float scale,
-                                    int n_splits, float* part_o, float* part_ml, int keep_first, int sink,
+                                    int n_splits, float* part_o, float* part_ml, int keep_first, int sink, const float* sink_val,
                                     cudaStream_t stream) {
     if (n_items <= 0) return 0;
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || nh > 65535 || page_tokens <= 0 || window < 0 || keep_first < 0)
@@ -400,7 +402,7 @@ extern "C" int locus_attn_chunk_mma(const void* q, const void* pool, void* out, 
     a.q = static_cast<const bf16*>(q); a.pool = static_cast<const bf16*>(pool); a.out = static_cast<bf16*>(out);
     a.seg_q0 = seg_q0; a.seg_qn = seg_qn; a.seg_ctx = seg_ctx; a.block_table = block_table;
     a.table_stride = table_stride; a.items = items; a.nh = nh; a.nkv = nkv; a.page_tokens = page_tokens;
-    a.window = window; a.scale = scale; a.keep_first = window > 0 ? keep_first : 0; a.sink = sink;
+    a.window = window; a.scale = scale; a.keep_first = window > 0 ? keep_first : 0; a.sink = sink; a.sink_val = sink ? sink_val : nullptr;
     a.n_splits = n_splits; a.part_o = part_o; a.part_ml = part_ml;
     switch (hd) {
         case 16: return launch<16>(a, n_items, stream);

@@ -28,6 +28,7 @@
 #include <string.h>
 
 #include "common.cuh"
+#include "sink.cuh"
 
 #define AT_HD 128        // head size
 #define AT_MQ 128        // queries per block
@@ -47,6 +48,7 @@ struct TcAttnArgs {
     int table_stride;
     const int* items;
     int nh, nkv, page_tokens, window;
+    const float* sink_val;  // with sink: a learned score per query head in its place (null: the score 0)
     int keep_first, sink;   // with a window: a request's first tokens stay in sight; one more term of score 0 in the denominator
     float scale;
     // Ranges of key tiles per block of queries (1: a block writes the result itself).  With more, a block takes
@@ -503,7 +505,7 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         {
             const float l = l_run + with_partner(n_tiles & 1, l_run);
             // the sink: one more term of score 0 (the sums are relative to 2^m_run); with ranges, the merge adds it
-            const float inv = 1.0f / (a.sink && a.n_splits == 1 ? l + exp2f(-m_run) : l);
+            const float inv = 1.0f / (a.sink && a.n_splits == 1 ? l + sink_term2(a.sink_val, h, m_run) : l);
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
                 uint32_t v[32];
@@ -584,7 +586,7 @@ __global__ void __launch_bounds__(128) attn_chunk_tc_merge_kernel(TcAttnArgs a) 
         acc.z += v[s].z * w;
         acc.w += v[s].w * w;
     }
-    if (a.sink) L += exp2f(-M);
+    if (a.sink) L += sink_term2(a.sink_val, h, M);
     const float inv = 1.0f / L;
     uint2 pk;
     pk.x = at_pack(acc.x * inv, acc.y * inv);
@@ -633,7 +635,8 @@ extern "C" int locus_attn_chunk_tc(const void* q, long long T, const void* pool,
                                    const int* seg_q0, const int* seg_qn, const int* seg_ctx, const int* block_table,
                                    int table_stride, const int* items, int n_items, int nh, int nkv, int hd,
                                    int page_tokens, int window, float scale, int n_splits, float* part_o,
-                                   float* part_ml, int keep_first, int sink, cudaStream_t stream) {
+                                   float* part_ml, int keep_first, int sink, const float* sink_val,
+                                   cudaStream_t stream) {
     if (n_items <= 0) return 0;
     if (n_splits < 1 || n_splits > AT_MAX_SPLITS) return LOCUS_ERR_UNSUPPORTED;
     if (n_splits > 1 && (part_o == nullptr || part_ml == nullptr ||
@@ -653,7 +656,7 @@ extern "C" int locus_attn_chunk_tc(const void* q, long long T, const void* pool,
     a.out = static_cast<bf16*>(out); a.seg_q0 = seg_q0; a.seg_qn = seg_qn; a.seg_ctx = seg_ctx;
     a.block_table = block_table; a.table_stride = table_stride; a.items = items; a.nh = nh; a.nkv = nkv;
     a.page_tokens = page_tokens; a.window = window; a.scale = scale;
-    a.keep_first = window > 0 ? keep_first : 0; a.sink = sink ? 1 : 0;
+    a.keep_first = window > 0 ? keep_first : 0; a.sink = sink ? 1 : 0; a.sink_val = sink ? sink_val : nullptr;
     a.n_splits = n_splits; a.part_o = part_o; a.part_ml = part_ml;
     const size_t smem = 7 * AT_TILE_BYTES + 160 + 2 * 2 * 128 * 4;
     static bool set = false;

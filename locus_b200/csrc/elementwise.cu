@@ -652,3 +652,170 @@ extern "C" int locus_stream_update(float* x, const float* y, const float* mix, c
     locus_launch(stream_update_kernel, n, 256, 0, stream, x, y, mix, out_coef, n_streams, H);
     return locus_launch_status();
 }
+
+// ---------------------------------------------------------------------------
+// Embedding with a second table addressed by a hash of the previous and the current token:
+//     out[t, :] = table[tok_t, :] + pair[r_t, :],   r_t = (prev_t * mul_prev + tok_t * mul_cur) mod buckets,
+// where prev_t is the token before tok_t in its request and r_t = buckets (the table's last row) for a request's first
+// token.  A segment's first token finds its predecessor in the request's state slot (`last` [n_slots, ld] int32, the
+// token that the step before ended on) unless it stands at position 0.  The hash is formed in 64-bit integers.  A second
+// small launch (pair_state_kernel) writes every segment's last token into its slot: it must not run beside the reads.
+#define EP_TOKENS 4   // tokens of a segment per block
+
+__global__ void __launch_bounds__(256) embed_pair_kernel(
+    const int* __restrict__ tokens, const int* __restrict__ positions, const void* __restrict__ table,
+    const void* __restrict__ pair, int table_dt, float* __restrict__ out, const int* __restrict__ seg_q0,
+    const int* __restrict__ seg_qn, const int* __restrict__ state_slots, const int* __restrict__ last, long long last_ld,
+    int H, long long buckets, long long mul_prev, long long mul_cur) {
+    pdl_entry();
+    pdl_trigger();
+    const int seg = blockIdx.y, qn = seg_qn[seg], q0 = seg_q0[seg];
+    for (int i = blockIdx.x * EP_TOKENS; i < min(qn, (blockIdx.x + 1) * EP_TOKENS); ++i) {
+        const int t = q0 + i;
+        const long long tok = tokens[t];
+        long long r = buckets;
+        if (positions[t] > 0) {
+            const long long prev = i > 0 ? tokens[t - 1] : last[static_cast<size_t>(state_slots[seg]) * last_ld];
+            r = (prev * mul_prev + tok * mul_cur) % buckets;
+        }
+        const size_t row = static_cast<size_t>(tok) * H, prow = static_cast<size_t>(r) * H;
+        float* o = out + static_cast<size_t>(t) * H;
+        for (int j = threadIdx.x; j < H; j += 256) o[j] = ld_dyn(table, table_dt, row + j) + ld_dyn(pair, table_dt, prow + j);
+    }
+}
+
+__global__ void pair_state_kernel(const int* __restrict__ tokens, const int* __restrict__ seg_q0,
+                                  const int* __restrict__ seg_qn, const int* __restrict__ state_slots,
+                                  int* __restrict__ last, long long last_ld, int n_seg) {
+    pdl_entry();
+    pdl_trigger();
+    const int seg = blockIdx.x * blockDim.x + threadIdx.x;
+    if (seg < n_seg && seg_qn[seg] > 0)
+        last[static_cast<size_t>(state_slots[seg]) * last_ld] = tokens[seg_q0[seg] + seg_qn[seg] - 1];
+}
+
+extern "C" int locus_embed_pair(const int* tokens, const int* positions, const void* table, const void* pair, int table_dt,
+                                float* out, const int* seg_q0, const int* seg_qn, const int* state_slots, int* last,
+                                long long last_ld, int n_seg, int longest_new, int H, long long buckets, long long mul_prev,
+                                long long mul_cur, cudaStream_t stream) {
+    if (n_seg <= 0 || longest_new <= 0) return 0;
+    if (buckets <= 0 || mul_prev < 0 || mul_cur < 0 || n_seg > 65535 || H <= 0) return LOCUS_ERR_UNSUPPORTED;
+    locus_launch(embed_pair_kernel, dim3((longest_new + EP_TOKENS - 1) / EP_TOKENS, n_seg), dim3(256), 0, stream, tokens,
+                 positions, table, pair, table_dt, out, seg_q0, seg_qn, state_slots, static_cast<const int*>(last), last_ld,
+                 H, buckets, mul_prev, mul_cur);
+    locus_launch(pair_state_kernel, dim3((n_seg + 63) / 64), dim3(64), 0, stream, tokens, seg_q0, seg_qn, state_slots, last,
+                 last_ld, n_seg);
+    return locus_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// The norm of a post-norm layer, in place on the float32 residual stream:
+//     u = alpha * x[i, :] + y[i, :];    x[i, :] = (u - mean(u)) / sqrt(mean((u - mean)^2) + eps) * w + b,
+// and, when `cast` is given, the new row once more in that buffer's element type (what the next sublayer reads).
+// One block per row; the mean first, then the squared deviations; every sum in an order that depends on H alone.
+template <typename TC>
+__global__ void __launch_bounds__(256) layernorm_post_kernel(float* __restrict__ x, const float* __restrict__ y, float alpha,
+                                                             const void* __restrict__ w, const void* __restrict__ b,
+                                                             int w_dt, float eps, TC* __restrict__ cast, int H) {
+    __shared__ float part[8];
+    pdl_entry();
+    pdl_trigger();
+    float* xr = x + static_cast<size_t>(blockIdx.x) * H;
+    const float* yr = y + static_cast<size_t>(blockIdx.x) * H;
+    auto u_at = [&](int j) { return fmaf(alpha, xr[j], yr[j]); };
+    float sum = 0.f;
+    for (int j = threadIdx.x; j < H; j += 256) sum += u_at(j);
+    const float mean = block_sum_256(sum, part) / static_cast<float>(H);
+    float ss = 0.f;
+    for (int j = threadIdx.x; j < H; j += 256) {
+        const float dlt = u_at(j) - mean;
+        ss = fmaf(dlt, dlt, ss);
+    }
+    const float scale = 1.0f / sqrtf(block_sum_256(ss, part) / static_cast<float>(H) + eps);
+    for (int j = threadIdx.x; j < H; j += 256) {
+        const float v = fmaf((u_at(j) - mean) * scale, ld_dyn(w, w_dt, j), ld_dyn(b, w_dt, j));
+        xr[j] = v;
+        if (cast) cast[static_cast<size_t>(blockIdx.x) * H + j] = from_f<TC>(v);
+    }
+}
+
+extern "C" int locus_layernorm_post(float* x, const float* y, float alpha, const void* w, const void* b, int w_dt, float eps,
+                                    void* cast, int cast_dt, int n, int H, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (H <= 0) return LOCUS_ERR_UNSUPPORTED;
+    if (cast != nullptr && cast_dt == LOCUS_DT_BF16)
+        locus_launch(layernorm_post_kernel<bf16>, n, 256, 0, stream, x, y, alpha, w, b, w_dt, eps, static_cast<bf16*>(cast), H);
+    else if (cast == nullptr || cast_dt == LOCUS_DT_F32)
+        locus_launch(layernorm_post_kernel<float>, n, 256, 0, stream, x, y, alpha, w, b, w_dt, eps, static_cast<float*>(cast), H);
+    else
+        return LOCUS_ERR_UNSUPPORTED;
+    return locus_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// RMS norm in place over up to two spans of columns of float32 rows, each span with a weight of its own:
+//     x[t, off : off + n] <- x[t, off : off + n] / sqrt(mean(x[t, off : off + n]^2) + eps) * w.
+// (A norm over a whole projection, all heads at once, of a row that holds several projections.)  Block (t, span).
+__global__ void __launch_bounds__(256) span_rmsnorm_kernel(float* __restrict__ x, int ld, int off0, int n0,
+                                                           const void* __restrict__ w0, int off1, int n1,
+                                                           const void* __restrict__ w1, int w_dt, float eps) {
+    __shared__ float part[8];
+    pdl_entry();
+    pdl_trigger();
+    const int off = blockIdx.y ? off1 : off0, n = blockIdx.y ? n1 : n0;
+    const void* w = blockIdx.y ? w1 : w0;
+    float* xr = x + static_cast<size_t>(blockIdx.x) * ld + off;
+    float ss = 0.f;
+    for (int j = threadIdx.x; j < n; j += 256) ss = fmaf(xr[j], xr[j], ss);
+    const float scale = 1.0f / sqrtf(block_sum_256(ss, part) / static_cast<float>(n) + eps);
+    for (int j = threadIdx.x; j < n; j += 256) xr[j] = xr[j] * scale * ld_dyn(w, w_dt, j);
+}
+
+extern "C" int locus_span_rmsnorm(float* x, int ld, int T, int off0, int n0, const void* w0, int off1, int n1, const void* w1,
+                                  int w_dt, float eps, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (n0 <= 0 || off0 < 0 || off0 + n0 > ld || (w1 != nullptr && (n1 <= 0 || off1 < 0 || off1 + n1 > ld)))
+        return LOCUS_ERR_UNSUPPORTED;
+    locus_launch(span_rmsnorm_kernel, dim3(T, w1 != nullptr ? 2 : 1), dim3(256), 0, stream, x, ld, off0, n0, w0, off1, n1, w1,
+                 w_dt, eps);
+    return locus_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// The activation of a clamped gated unit over float32 rows [g | u] (row stride ld; g the first I columns, u the next I:
+// the two products of the same input, made as one):
+//     g' = min(s g, limit),  u' = clamp(s u, -limit, limit),  out = g' sigmoid(1.702 g') (u' + 1),
+// with s = row_scale[scale_rows ? scale_rows[m] : m] (a weight on the unit's INPUT, which both products carry as a
+// factor; null: 1).
+template <typename TO>
+__global__ void __launch_bounds__(256) glu_clamp_kernel(const float* __restrict__ gu, long long ld,
+                                                        const float* __restrict__ row_scale,
+                                                        const int* __restrict__ scale_rows, float limit,
+                                                        TO* __restrict__ out, int I, long long total) {
+    pdl_entry();
+    pdl_trigger();
+    const long long i = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
+    if (i >= total) return;
+    const long long m = i / I;
+    const float s = row_scale ? row_scale[scale_rows ? scale_rows[m] : m] : 1.0f;
+    const float* row = gu + m * ld + (i - m * I);
+    const float gv = fminf(row[0] * s, limit), uv = fminf(fmaxf(row[I] * s, -limit), limit);
+    out[i] = from_f<TO>(gv / (1.0f + expf(-1.702f * gv)) * (uv + 1.0f));
+}
+
+extern "C" int locus_glu_clamp(const float* gu, long long ld, const float* row_scale, const int* scale_rows, float limit,
+                               void* out, int out_dt, int n, int I, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (I <= 0 || ld < 2LL * I) return LOCUS_ERR_UNSUPPORTED;
+    const long long total = static_cast<long long>(n) * I, blocks = (total + 255) / 256;
+    if (blocks > 0x7fffffffLL) return LOCUS_ERR_UNSUPPORTED;
+    if (out_dt == LOCUS_DT_BF16)
+        locus_launch(glu_clamp_kernel<bf16>, dim3(static_cast<unsigned>(blocks)), dim3(256), 0, stream, gu, ld, row_scale,
+                     scale_rows, limit, static_cast<bf16*>(out), I, total);
+    else if (out_dt == LOCUS_DT_F32)
+        locus_launch(glu_clamp_kernel<float>, dim3(static_cast<unsigned>(blocks)), dim3(256), 0, stream, gu, ld, row_scale,
+                     scale_rows, limit, static_cast<float*>(out), I, total);
+    else
+        return LOCUS_ERR_UNSUPPORTED;
+    return locus_launch_status();
+}

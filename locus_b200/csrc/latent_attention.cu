@@ -25,7 +25,9 @@
 //
 // Angles: position * frequency and its sine and cosine are formed in float64 from float64 frequencies (the
 // host computes them, ramp of a long-context scaling included) and rounded once; `magnitude` multiplies both.
-// Pairs are interleaved: (2i, 2i + 1), i < rot_pairs; elements behind 2 * rot_pairs pass unchanged.
+// Pairs are interleaved, (2i, 2i + 1), or with `half_split` the halves of the turned stretch, (i, i + rot_pairs);
+// i < rot_pairs; elements behind 2 * rot_pairs pass unchanged.  q_rank = 0: no query latent (the queries are projected
+// elsewhere), the row holds the key/value side alone.
 #include "common.cuh"
 
 __device__ __forceinline__ float block_sum_256(float v, float* part) {
@@ -40,7 +42,8 @@ __device__ __forceinline__ float block_sum_256(float v, float* part) {
 }
 
 // ---------------------------------------------------------------------------
-// dqkv [T, q_rank + kv_rank + rot_dim] float32: the stacked down-projections of a token.
+// dqkv [T, ld] float32, of which the first q_rank + kv_rank + rot_dim columns are the stacked down-projections of a
+// token (write = 0: the first q_rank alone).
 //   cq[t]            = rmsnorm(dqkv[t, :q_rank]) * wq                       -> cq_out [T, q_rank]
 //   row[:kv_rank]    = rmsnorm(dqkv[t, q_rank : q_rank + kv_rank]) * wkv    -> the token's cache row
 //   row[kv_rank:]    = rotate(dqkv[t, q_rank + kv_rank :], position)
@@ -49,19 +52,19 @@ __global__ void __launch_bounds__(256) latent_prep_kernel(
     const float* __restrict__ dqkv, const int* __restrict__ positions, const double* __restrict__ freq,
     float magnitude, const TW* __restrict__ wq, const TW* __restrict__ wkv, float eps, TO* __restrict__ cq_out,
     TO* __restrict__ pool, const int* __restrict__ slots, int q_rank, int kv_rank, int rot_dim, int rot_pairs,
-    int write) {
+    int write, int half_split, int ld) {
     __shared__ float part[8];
     pdl_entry();
     pdl_trigger();
     const int t = blockIdx.x;
-    const int width = q_rank + kv_rank + rot_dim;
-    const float* src = dqkv + static_cast<size_t>(t) * width;
+    const float* src = dqkv + static_cast<size_t>(t) * ld;
     float sq = 0.f, sk = 0.f;
     for (int j = threadIdx.x; j < q_rank; j += 256) sq = fmaf(src[j], src[j], sq);
-    for (int j = threadIdx.x; j < kv_rank; j += 256) sk = fmaf(src[q_rank + j], src[q_rank + j], sk);
+    if (write)
+        for (int j = threadIdx.x; j < kv_rank; j += 256) sk = fmaf(src[q_rank + j], src[q_rank + j], sk);
     sq = block_sum_256(sq, part);
     sk = block_sum_256(sk, part);
-    const float scale_q = 1.0f / sqrtf(sq / static_cast<float>(q_rank) + eps);
+    const float scale_q = q_rank > 0 ? 1.0f / sqrtf(sq / static_cast<float>(q_rank) + eps) : 0.f;
     const float scale_k = 1.0f / sqrtf(sk / static_cast<float>(kv_rank) + eps);
     TO* cq = cq_out + static_cast<size_t>(t) * q_rank;
     for (int j = threadIdx.x; j < q_rank; j += 256) cq[j] = from_f<TO>(src[j] * scale_q * to_f(wq[j]));
@@ -74,9 +77,10 @@ __global__ void __launch_bounds__(256) latent_prep_kernel(
         double s, c;
         sincos(pos * freq[i], &s, &c);
         const float cs = static_cast<float>(c) * magnitude, sn = static_cast<float>(s) * magnitude;
-        const float u = kr[2 * i], v = kr[2 * i + 1];
-        row[kv_rank + 2 * i] = from_f<TO>(u * cs - v * sn);
-        row[kv_rank + 2 * i + 1] = from_f<TO>(v * cs + u * sn);
+        const int i0 = half_split ? i : 2 * i, i1 = half_split ? i + rot_pairs : 2 * i + 1;
+        const float u = kr[i0], v = kr[i1];
+        row[kv_rank + i0] = from_f<TO>(u * cs - v * sn);
+        row[kv_rank + i1] = from_f<TO>(v * cs + u * sn);
     }
     for (int j = 2 * rot_pairs + threadIdx.x; j < rot_dim; j += 256) row[kv_rank + j] = from_f<TO>(kr[j]);
 }
@@ -84,14 +88,15 @@ __global__ void __launch_bounds__(256) latent_prep_kernel(
 extern "C" int locus_latent_prep(const float* dqkv, const int* positions, const double* freq, float magnitude,
                                  const void* wq, const void* wkv, int w_dt, float eps, void* cq_out, void* pool,
                                  int dt, const int* slots, int T, int q_rank, int kv_rank, int rot_dim,
-                                 int rot_pairs, int write, cudaStream_t stream) {
+                                 int rot_pairs, int write, int half_split, int ld, cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (q_rank <= 0 || kv_rank <= 0 || rot_dim < 0 || rot_pairs < 0 || 2 * rot_pairs > rot_dim) return LOCUS_ERR_UNSUPPORTED;
+    if (ld < q_rank + (write ? kv_rank + rot_dim : 0)) return LOCUS_ERR_UNSUPPORTED;
+    if (q_rank < 0 || kv_rank <= 0 || rot_dim < 0 || rot_pairs < 0 || 2 * rot_pairs > rot_dim) return LOCUS_ERR_UNSUPPORTED;
     if (rot_pairs > 0 && freq == nullptr) return LOCUS_ERR_UNSUPPORTED;
 #define PREP(TO, TW)                                                                                              \
     locus_launch(latent_prep_kernel<TO, TW>, T, 256, 0, stream, dqkv, positions, freq, magnitude,                  \
                  static_cast<const TW*>(wq), static_cast<const TW*>(wkv), eps, static_cast<TO*>(cq_out),           \
-                 static_cast<TO*>(pool), slots, q_rank, kv_rank, rot_dim, rot_pairs, write)
+                 static_cast<TO*>(pool), slots, q_rank, kv_rank, rot_dim, rot_pairs, write, half_split, ld)
     if (dt == LOCUS_DT_BF16 && w_dt == LOCUS_DT_BF16) PREP(bf16, bf16);
     else if (dt == LOCUS_DT_F32 && w_dt == LOCUS_DT_F32) PREP(float, float);
     else if (dt == LOCUS_DT_F32 && w_dt == LOCUS_DT_BF16) PREP(float, bf16);
@@ -108,7 +113,7 @@ extern "C" int locus_latent_prep(const float* dqkv, const int* positions, const 
 template <typename TA>
 __global__ void __launch_bounds__(256) latent_q_split_kernel(
     const TA* __restrict__ q, const int* __restrict__ positions, const double* __restrict__ freq, float magnitude,
-    TA* __restrict__ q_nope_hm, TA* __restrict__ q_rot, int T, int H, int dn, int dr, int rot_pairs) {
+    TA* __restrict__ q_nope_hm, TA* __restrict__ q_rot, int T, int H, int dn, int dr, int rot_pairs, int half_split) {
     extern __shared__ float cs_tab[];  // [rot_pairs][2]
     pdl_entry();
     pdl_trigger();
@@ -128,6 +133,22 @@ __global__ void __launch_bounds__(256) latent_q_split_kernel(
         q_nope_hm[(static_cast<size_t>(h) * T + t) * dn + d] = src[h * hw + d];
     }
     TA* dst = q_rot + static_cast<size_t>(t) * H * dr;
+    if (half_split) {
+        // element e < rot_pairs is the first of its pair, rot_pairs <= e < 2 rot_pairs the second; the rest pass
+        for (int i = threadIdx.x; i < H * dr; i += 256) {
+            const int h = i / dr, e = i % dr;
+            const TA* hs = src + h * hw + dn;
+            float val = to_f(hs[e]);
+            if (e < 2 * rot_pairs) {
+                const int p = e < rot_pairs ? e : e - rot_pairs;
+                const float u = to_f(hs[p]), v = to_f(hs[p + rot_pairs]);
+                const float cs = cs_tab[2 * p], sn = cs_tab[2 * p + 1];
+                val = e < rot_pairs ? u * cs - v * sn : v * cs + u * sn;
+            }
+            dst[i] = from_f<TA>(val);
+        }
+        return;
+    }
     const int half = dr / 2;  // pairs of a head, turned or not
     for (int i = threadIdx.x; i < H * half; i += 256) {
         const int h = i / half, p = i % half;
@@ -147,7 +168,7 @@ __global__ void __launch_bounds__(256) latent_q_split_kernel(
 
 extern "C" int locus_latent_q_split(const void* q, int dt, const int* positions, const double* freq,
                                     float magnitude, void* q_nope_hm, void* q_rot, int T, int H, int dn, int dr,
-                                    int rot_pairs, cudaStream_t stream) {
+                                    int rot_pairs, int half_split, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (H <= 0 || dn <= 0 || dr < 0 || rot_pairs < 0 || 2 * rot_pairs > dr) return LOCUS_ERR_UNSUPPORTED;
     if (rot_pairs > 0 && freq == nullptr) return LOCUS_ERR_UNSUPPORTED;
@@ -155,10 +176,10 @@ extern "C" int locus_latent_q_split(const void* q, int dt, const int* positions,
     if (smem > 48 * 1024) return LOCUS_ERR_UNSUPPORTED;
     if (dt == LOCUS_DT_BF16)
         locus_launch(latent_q_split_kernel<bf16>, T, 256, smem, stream, static_cast<const bf16*>(q), positions, freq,
-                     magnitude, static_cast<bf16*>(q_nope_hm), static_cast<bf16*>(q_rot), T, H, dn, dr, rot_pairs);
+                     magnitude, static_cast<bf16*>(q_nope_hm), static_cast<bf16*>(q_rot), T, H, dn, dr, rot_pairs, half_split);
     else if (dt == LOCUS_DT_F32)
         locus_launch(latent_q_split_kernel<float>, T, 256, smem, stream, static_cast<const float*>(q), positions, freq,
-                     magnitude, static_cast<float*>(q_nope_hm), static_cast<float*>(q_rot), T, H, dn, dr, rot_pairs);
+                     magnitude, static_cast<float*>(q_nope_hm), static_cast<float*>(q_rot), T, H, dn, dr, rot_pairs, half_split);
     else
         return LOCUS_ERR_UNSUPPORTED;
     return locus_launch_status();

@@ -459,7 +459,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, w2: Optional[
     ``second_tiles``: a grouped product on the tensor cores walks the layout's second tile list (``moe_sort`` with
     ``tile2_m``) instead of the first.
     """
-    _cuda_c(x, "x")
+    # (x may be a stretch of columns of wider rows: the kernels take its row stride)
+    _need(x.is_cuda and x.stride(-1) == 1 and (x.is_contiguous() or x.dim() == 2), "linear: x must be CUDA rows with unit stride")
     _cuda_c(w, "w")
     _cuda_c(out, "out")
     K = x.shape[-1]
@@ -606,14 +607,25 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, inv_freq: Optional
     _check(code, "rope_kv_write")
 
 
+def _sink_args(sink, n_heads: int):
+    """(flag, pointer) of a softmax sink for the attention entry points: ``sink`` is False (none), True (one more term of
+    score 0) or a float32 tensor [n_heads] of learned scores."""
+    if isinstance(sink, torch.Tensor):
+        _need(sink.is_cuda and sink.dtype == torch.float32 and sink.is_contiguous() and sink.numel() == n_heads,
+              "attention: a learned sink must be float32 [n_heads] on the device")
+        return I(1), _p(sink)
+    return I(1 if sink else 0), None
+
+
 def attn_chunk(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, *, seg_q0: torch.Tensor,
                seg_qn: torch.Tensor, seg_ctx: torch.Tensor, block_table: torch.Tensor,
                items: torch.Tensor, n_items: int, n_heads: int, n_kv_heads: int, head_dim: int,
-               page_tokens: int, window: int, scale: float, keep_first: int = 0, sink: bool = False) -> None:
+               page_tokens: int, window: int, scale: float, keep_first: int = 0, sink=False) -> None:
     """Attention of portions of prompts: ``items`` [n_items, 2] = (segment, first query of a
     16-query tile).  Keys come from the cache through ``block_table`` [n_seg, width].  ``keep_first``: with a
     window, a request's first that many tokens stay in sight of every later query; ``sink``: the softmax has one
-    more term of score 0 and no value in its denominator."""
+    more term in its denominator that has no value: True for the score 0, a float32 tensor [n_heads] for a learned
+    score per head (taken as it is, not multiplied by ``scale``)."""
     _cuda_c(q, "q")
     _cuda_c(out, "out")
     _cuda_c(pool, "pool")
@@ -623,7 +635,7 @@ def attn_chunk(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, *, seg_q0
     code = _lib("attention").locus_attn_chunk(
         _p(q), I(dtype_code(q.dtype)), _p(pool), _p(out), _p(seg_q0), _p(seg_qn), _p(seg_ctx),
         _p(block_table), I(block_table.shape[1]), _p(items), I(n_items), I(n_heads), I(n_kv_heads),
-        I(head_dim), I(page_tokens), I(window), F(scale), I(keep_first), I(1 if sink else 0), _stream()
+        I(head_dim), I(page_tokens), I(window), F(scale), I(keep_first), *_sink_args(sink, n_heads), _stream()
     )
     _check(code, "attn_chunk", f"(heads {n_heads}/{n_kv_heads}, head_dim {head_dim})")
 
@@ -666,7 +678,7 @@ def attn_chunk_mma(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, *, se
                    items: torch.Tensor, n_items: int, n_heads: int, n_kv_heads: int, head_dim: int,
                    page_tokens: int, window: int, scale: float, n_splits: int = 1,
                    part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None,
-                   keep_first: int = 0, sink: bool = False) -> None:
+                   keep_first: int = 0, sink=False) -> None:
     """Attention of portions of prompts on the tensor cores: ``items`` [n_items, 2] =
     (segment, first query of a 64-query tile); otherwise as :func:`attn_chunk`.  ``n_splits`` > 1
     (:func:`attn_chunk_mma_splits`) with scratch of :func:`attn_chunk_mma_scratch` floats: the keys of
@@ -686,7 +698,7 @@ def attn_chunk_mma(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, *, se
         _p(q), _p(pool), _p(out), _p(seg_q0), _p(seg_qn), _p(seg_ctx), _p(block_table), I(block_table.shape[1]),
         _p(items), I(n_items), I(n_heads), I(n_kv_heads), I(head_dim), I(page_tokens), I(window), F(scale),
         I(n_splits), _p(part_o if n_splits > 1 else None), _p(part_ml if n_splits > 1 else None), I(keep_first),
-        I(1 if sink else 0), _stream()
+        *_sink_args(sink, n_heads), _stream()
     )
     if n_splits > 1 and code == 0:
         _count_launches(1)
@@ -739,7 +751,7 @@ def attn_chunk_tc(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, *, seg
                   items: torch.Tensor, n_items: int, n_heads: int, n_kv_heads: int, head_dim: int,
                   page_tokens: int, window: int, scale: float, n_splits: int = 1,
                   part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None,
-                  keep_first: int = 0, sink: bool = False) -> None:
+                  keep_first: int = 0, sink=False) -> None:
     """Attention of portions of prompts with tcgen05 tensor cores (scores and sums in tensor memory):
     ``items`` as for :func:`attn_chunk_mma` (tiles of 64 queries; a block takes an even one and the 64 queries
     behind it).  ``n_splits`` > 1 (:func:`attn_chunk_tc_splits`) with scratch of :func:`attn_chunk_tc_scratch`
@@ -763,7 +775,7 @@ def attn_chunk_tc(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, *, seg
         _p(q), LL(q.shape[0]), _p(pool), LL(pool.shape[0]), _p(out), _p(seg_q0), _p(seg_qn), _p(seg_ctx),
         _p(block_table), I(block_table.shape[1]), _p(items), I(n_items), I(n_heads), I(n_kv_heads), I(head_dim),
         I(page_tokens), I(window), F(scale), I(n_splits), _p(part_o if n_splits > 1 else None),
-        _p(part_ml if n_splits > 1 else None), I(keep_first if window > 0 else 0), I(1 if sink else 0), _stream()
+        _p(part_ml if n_splits > 1 else None), I(keep_first if window > 0 else 0), *_sink_args(sink, n_heads), _stream()
     )
     if n_splits > 1 and code == 0:
         _count_launches(1)
@@ -868,7 +880,7 @@ def attn_decode(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, *, seg_q
                 items: torch.Tensor, n_items: int, n_heads: int, n_kv_heads: int, head_dim: int,
                 page_tokens: int, window: int, scale: float, part_o: torch.Tensor,
                 part_ml: torch.Tensor, counters: torch.Tensor, max_splits: int, keep_first: int = 0,
-                sink: bool = False) -> None:
+                sink=False) -> None:
     """Attention of single new tokens: ``items`` [n_items] = segments with one new token.  ``keep_first``, ``sink``
     as for :func:`attn_chunk` (the streaming kernels, per head and per group of query heads, walk the kept tokens in front
     of the window as one more range of the request and want scratch for two ranges per request and head, the kernel whose
@@ -897,7 +909,7 @@ def attn_decode(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, *, seg_q
             _p(q), _p(pool), _p(out), _p(seg_q0), _p(seg_ctx), _p(block_table), I(block_table.shape[1]), _p(items),
             I(n_items), I(n_heads), I(n_kv_heads), I(head_dim), I(page_tokens), I(window), F(scale), _p(part_o),
             _p(part_ml), _p(counters), ctypes.c_longlong(max_units), I(GQA_COST_RANGE),
-            I(GQA_COST_MERGE_PER_HEAD * (n_heads // n_kv_heads)), I(keep_first if window > 0 else 0), I(1 if sink else 0),
+            I(GQA_COST_MERGE_PER_HEAD * (n_heads // n_kv_heads)), I(keep_first if window > 0 else 0), *_sink_args(sink, n_heads),
             _stream()
         )
         _check(code, "attn_decode", f"(grouped queries; heads {n_heads}/{n_kv_heads}, head_dim {head_dim})")
@@ -906,7 +918,7 @@ def attn_decode(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, *, seg_q
         _p(q), I(dtype_code(q.dtype)), _p(pool), _p(out), _p(seg_q0), _p(seg_qn), _p(seg_ctx),
         _p(block_table), I(block_table.shape[1]), _p(items), I(n_items), I(n_heads), I(n_kv_heads),
         I(head_dim), I(page_tokens), I(window), F(scale), _p(part_o), _p(part_ml), _p(counters), I(max_splits),
-        ctypes.c_longlong(max_units), I(keep_first if window > 0 else 0), I(1 if sink else 0), _stream()
+        ctypes.c_longlong(max_units), I(keep_first if window > 0 else 0), *_sink_args(sink, n_heads), _stream()
     )
     _check(code, "attn_decode", f"(heads {n_heads}/{n_kv_heads}, head_dim {head_dim})")
 
@@ -1198,35 +1210,37 @@ def _freq(freq: Optional[torch.Tensor], rot_pairs: int, what: str) -> None:
 def latent_prep(dqkv: torch.Tensor, positions: torch.Tensor, freq: Optional[torch.Tensor], magnitude: float,
                 w_q: torch.Tensor, w_kv: torch.Tensor, eps: float, cq_out: torch.Tensor, pool: torch.Tensor,
                 slots: torch.Tensor, *, q_rank: int, kv_rank: int, rot_dim: int, rot_pairs: int,
-                write: bool = True) -> None:
+                write: bool = True, half_split: bool = False) -> None:
     """From the stacked down-projections ``dqkv`` [T, q_rank + kv_rank + rot_dim] (float32): the normed query
     latent into ``cq_out`` [T, q_rank]; the normed key/value latent and the rotated shared key part into the
     token's cache row (``pool`` [n_pages, 1, 1, page_tokens, kv_rank + rot_dim], ``slots[t]`` = page *
     page_tokens + offset).  Interleaved pairs (2i, 2i + 1), i < ``rot_pairs``, are turned by
-    position * freq[i]; cosine and sine are multiplied by ``magnitude``."""
-    _cuda_c(dqkv, "dqkv")
-    _cuda_c(cq_out, "cq_out")
+    position * freq[i]; cosine and sine are multiplied by ``magnitude``.  ``half_split``: the pairs are (i, i +
+    rot_pairs) instead.  ``q_rank`` 0: no query latent (``cq_out``, ``w_q`` None): the rows hold the key/value side alone."""
+    _need(dqkv.is_cuda and dqkv.stride(1) == 1, "latent_prep: dqkv must be CUDA rows with unit stride")
+    if q_rank > 0:
+        _cuda_c(cq_out, "cq_out")
     _cuda_c(pool, "pool")
     _i32(positions, "positions")
     _i32(slots, "slots")
     T = dqkv.shape[0]
-    _need(dqkv.dtype == torch.float32 and dqkv.shape[1] == q_rank + kv_rank + rot_dim, "latent_prep: dqkv float32 of the stacked width")
-    _need(cq_out.dtype == pool.dtype and cq_out.shape[0] >= T and cq_out.shape[1] == q_rank, "latent_prep: cq_out")
+    _need(dqkv.dtype == torch.float32 and dqkv.shape[1] >= q_rank + (kv_rank + rot_dim if write else 0), "latent_prep: dqkv float32 of the stacked width")
+    _need(q_rank == 0 or (cq_out.dtype == pool.dtype and cq_out.shape[0] >= T and cq_out.shape[1] == q_rank), "latent_prep: cq_out")
     _need(pool.shape[-1] == kv_rank + rot_dim and pool.shape[1] == 1 and pool.shape[2] == 1, "latent_prep: pool layout")
-    _need(w_q.dtype == w_kv.dtype and w_q.numel() == q_rank and w_kv.numel() == kv_rank and w_q.is_cuda and w_kv.is_cuda,
-          "latent_prep: norm weights")
+    _need(w_kv.numel() == kv_rank and w_kv.is_cuda and (q_rank == 0 or (w_q.dtype == w_kv.dtype and w_q.numel() == q_rank
+                                                                     and w_q.is_cuda)), "latent_prep: norm weights")
     _need(positions.numel() >= T and slots.numel() >= T, "latent_prep: T mismatch")
     _freq(freq, rot_pairs, "latent_prep")
     code = _lib("latent_attention").locus_latent_prep(
-        _p(dqkv), _p(positions), _p(freq), F(magnitude), _p(w_q), _p(w_kv), I(dtype_code(w_q.dtype)), F(eps),
-        _p(cq_out), _p(pool), I(dtype_code(pool.dtype)), _p(slots), I(T), I(q_rank), I(kv_rank), I(rot_dim),
-        I(rot_pairs), I(1 if write else 0), _stream())
+        _p(dqkv), _p(positions), _p(freq), F(magnitude), _p(w_q if q_rank else None), _p(w_kv), I(dtype_code(w_kv.dtype)), F(eps),
+        _p(cq_out if q_rank else None), _p(pool), I(dtype_code(pool.dtype)), _p(slots), I(T), I(q_rank), I(kv_rank), I(rot_dim),
+        I(rot_pairs), I(1 if write else 0), I(1 if half_split else 0), I(dqkv.stride(0)), _stream())
     _check(code, "latent_prep")
 
 
 def latent_q_split(q: torch.Tensor, positions: torch.Tensor, freq: Optional[torch.Tensor], magnitude: float,
                    q_nope_hm: torch.Tensor, q_rot: torch.Tensor, *, n_heads: int, nope_dim: int, rot_dim: int,
-                   rot_pairs: int) -> None:
+                   rot_pairs: int, half_split: bool = False) -> None:
     """``q`` [T, H * (nope_dim + rot_dim)], head by head [unrotated | rotated]: the unrotated parts go to
     ``q_nope_hm`` [H * T, nope_dim] (head-major: row h * T + t), the rotated parts, turned by the token's
     position, to ``q_rot`` [T, H * rot_dim]."""
@@ -1241,7 +1255,7 @@ def latent_q_split(q: torch.Tensor, positions: torch.Tensor, freq: Optional[torc
     _freq(freq, rot_pairs, "latent_q_split")
     code = _lib("latent_attention").locus_latent_q_split(
         _p(q), I(dtype_code(q.dtype)), _p(positions), _p(freq), F(magnitude), _p(q_nope_hm), _p(q_rot), I(T),
-        I(n_heads), I(nope_dim), I(rot_dim), I(rot_pairs), _stream())
+        I(n_heads), I(nope_dim), I(rot_dim), I(rot_pairs), I(1 if half_split else 0), _stream())
     _check(code, "latent_q_split")
 
 
@@ -1784,6 +1798,124 @@ def delta_out(o: torch.Tensor, proj: torch.Tensor, off_g: int, w: torch.Tensor, 
                                               I(v_dim), _stream())
     _check(code, "delta_out")
 
+
+
+# ---------------------------------------------------------------------------
+# an embedding with a hashed pair table, the norm of a post-norm layer, a norm over spans of columns, a clamped gated
+# unit (csrc/elementwise.cu); gated linear attention (csrc/gla.cu)
+
+
+def embed_pair(tokens: torch.Tensor, positions: torch.Tensor, table: torch.Tensor, pair: torch.Tensor, out: torch.Tensor, *,
+               seg_q0: torch.Tensor, seg_qn: torch.Tensor, state_slots: torch.Tensor, last: torch.Tensor, n_seg: int,
+               longest_new: int, mul_prev: int, mul_cur: int) -> None:
+    """out[t] = table[tok_t] + pair[r_t] as float32, r_t = (prev_t * mul_prev + tok_t * mul_cur) mod buckets with
+    buckets = rows of ``pair`` - 1, and r_t = buckets for a token at position 0.  The token before a segment's first one
+    is read from ``last`` [n_slots, 1] int32 at the request's state slot; afterwards every segment's last token is
+    written there (a second launch)."""
+    _i32(tokens, "tokens")
+    _i32(positions, "positions")
+    _cuda_c(table, "table")
+    _cuda_c(pair, "pair")
+    _cuda_c(out, "out")
+    H = table.shape[1]
+    _need(out.dtype == torch.float32 and out.shape[1] == H and pair.shape[1] == H and pair.dtype == table.dtype
+          and pair.shape[0] >= 2, "embed_pair: tables and out")
+    _need(last.is_cuda and last.dtype == torch.int32 and last.dim() == 2 and last.stride(1) == 1, "embed_pair: last [n_slots, 1] int32")
+    code = _lib("elementwise").locus_embed_pair(
+        _p(tokens), _p(positions), _p(table), _p(pair), I(dtype_code(table.dtype)), _p(out), _p(seg_q0), _p(seg_qn),
+        _p(state_slots), _p(last), LL(last.stride(0)), I(n_seg), I(longest_new), I(H), LL(pair.shape[0] - 1), LL(mul_prev),
+        LL(mul_cur), _stream())
+    if code == 0:
+        _count_launches(1)   # the launch that moves the slots on
+    _check(code, "embed_pair")
+
+
+def layernorm_post(x: torch.Tensor, y: torch.Tensor, alpha: float, w: torch.Tensor, b: torch.Tensor, eps: float,
+                   cast: Optional[torch.Tensor] = None) -> None:
+    """x <- layer_norm(alpha * x + y) * w + b in place on float32 rows (mean and variance in float32); ``cast``: the new
+    rows once more in that buffer's element type."""
+    _f32c(x, "layernorm_post: x")
+    _f32c(y, "layernorm_post: y")
+    _cuda_c(w, "w")
+    _cuda_c(b, "b")
+    n, H = x.shape
+    _need(x.is_contiguous() and y.is_contiguous() and y.shape[0] >= n and y.shape[1] == H and w.numel() == H
+          and b.numel() == H and w.dtype == b.dtype, "layernorm_post: shapes")
+    if cast is not None:
+        _cuda_c(cast, "cast")
+        _need(cast.shape[0] >= n and cast.shape[1] == H, "layernorm_post: cast")
+    code = _lib("elementwise").locus_layernorm_post(
+        _p(x), _p(y), F(alpha), _p(w), _p(b), I(dtype_code(w.dtype)), F(eps), _p(cast),
+        I(dtype_code(cast.dtype) if cast is not None else 0), I(n), I(H), _stream())
+    _check(code, "layernorm_post")
+
+
+def span_rmsnorm(x: torch.Tensor, spans, eps: float) -> None:
+    """RMS norm in place over spans of columns of the float32 rows ``x``: ``spans`` = one or two (offset, width, weight
+    [width]); each span is divided by its own root mean square and multiplied by its weight."""
+    _f32c(x, "span_rmsnorm: x")
+    _need(1 <= len(spans) <= 2 and x.stride(1) == 1, "span_rmsnorm: one or two spans")
+    (o0, n0, w0), (o1, n1, w1) = spans[0], (spans[1] if len(spans) > 1 else (0, 0, None))
+    for w, n in ((w0, n0), (w1, n1)):
+        if w is not None:
+            _cuda_c(w, "w")
+            _need(w.numel() == n and w.dtype == w0.dtype, "span_rmsnorm: weights")
+    code = _lib("elementwise").locus_span_rmsnorm(_p(x), I(x.stride(0)), I(x.shape[0]), I(o0), I(n0), _p(w0), I(o1), I(n1),
+                                                  _p(w1), I(dtype_code(w0.dtype)), F(eps), _stream())
+    _check(code, "span_rmsnorm")
+
+
+def glu_clamp(gu: torch.Tensor, limit: float, out: torch.Tensor, *, n_rows: Optional[int] = None,
+              row_scale: Optional[torch.Tensor] = None, scale_rows: Optional[torch.Tensor] = None) -> None:
+    """out = g' sigmoid(1.702 g') (u' + 1) with g' = min(s g, limit), u' = clamp(s u, -limit, limit) over float32 rows
+    ``gu`` [n, 2 I] = [g | u]; s = row_scale[scale_rows[m] if scale_rows else m] (a weight on the unit's input, which
+    both products carry as a factor; None: 1)."""
+    _f32c(gu, "glu_clamp: gu")
+    _cuda_c(out, "out")
+    n = out.shape[0] if n_rows is None else n_rows
+    inter = out.shape[1]
+    _need(gu.dim() == 2 and gu.shape[1] == 2 * inter and gu.shape[0] >= n and out.shape[0] >= n, "glu_clamp: shapes")
+    if row_scale is not None:
+        _need(row_scale.dtype == torch.float32 and row_scale.is_contiguous(), "glu_clamp: row_scale must be float32")
+        if scale_rows is not None:
+            _i32(scale_rows, "scale_rows")
+    code = _lib("elementwise").locus_glu_clamp(_p(gu), LL(gu.stride(0)), _p(row_scale),
+                                               _p(scale_rows if row_scale is not None else None), F(limit), _p(out),
+                                               I(dtype_code(out.dtype)), I(n), I(inter), _stream())
+    _check(code, "glu_clamp")
+
+
+GLA_MAX_DIM = 256
+
+
+def gla_decay(z: torch.Tensor, off: int, n: int, tau: float) -> None:
+    """z[:, off : off + n] <- sigmoid(z)^(1 / tau) in place on float32 rows, as exp(-softplus(-z) / tau)."""
+    _f32c(z, "gla_decay: z")
+    _need(z.stride(1) == 1 and 0 <= off and off + n <= z.shape[1], "gla_decay: columns")
+    code = _lib("gla").locus_gla_decay(_p(z), I(z.stride(0)), I(off), I(n), I(z.shape[0]), F(tau), _stream())
+    _check(code, "gla_decay")
+
+
+def gla_scan(q: torch.Tensor, off_q: int, k: torch.Tensor, off_k: int, v: torch.Tensor, off_v: int, decay: torch.Tensor,
+             off_a: int, state: torch.Tensor, state_offset: int, state_slots: torch.Tensor, seg_q0: torch.Tensor,
+             seg_qn: torch.Tensor, n_seg: int, out: torch.Tensor, *, n_heads: int, dim: int, v_dim: int, q_scale: float) -> None:
+    """Gated linear attention per request and head over every segment's new tokens in order, from and into the request's
+    state slot: S <- diag(a_t) S + k_t v_t^T; o_t = S^T q_t * q_scale.  ``q``, ``k``, ``decay`` (a_t, one factor per key
+    channel) and ``v``: float32 row matrices in which head h's columns start at ``off_*`` + h * dim (``off_v`` + h * v_dim);
+    head h's state [dim, v_dim] starts ``state_offset`` + h * dim * v_dim floats into a slot of ``state`` [n_slots,
+    floats]; ``out`` [T, n_heads * v_dim] float32."""
+    for t, name in ((q, "q"), (k, "k"), (v, "v"), (decay, "decay"), (out, "out")):
+        _f32c(t, f"gla_scan: {name}")
+    _i32(state_slots, "state_slots")
+    _need(state.is_cuda and state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1
+          and state_offset + n_heads * dim * v_dim <= state.shape[1], "gla_scan: the state does not hold the heads")
+    _need(out.shape[1] == n_heads * v_dim and dim <= GLA_MAX_DIM, "gla_scan: out [T, n_heads * v_dim], dim <= 256")
+    code = _lib("gla").locus_gla_scan(
+        _p(q), I(q.stride(0)), I(off_q), _p(k), I(k.stride(0)), I(off_k), _p(v), I(v.stride(0)), I(off_v), _p(decay),
+        I(decay.stride(0)), I(off_a), ctypes.c_void_p(state.data_ptr() + 4 * state_offset), LL(state.stride(0)),
+        _p(state_slots), _p(seg_q0), _p(seg_qn), I(n_seg), _p(out), I(out.stride(0)), I(n_heads), I(dim), I(v_dim),
+        F(q_scale), _stream())
+    _check(code, "gla_scan", f"(heads {n_heads}, dim {dim}, v_dim {v_dim})")
 
 
 def apply_penalties(logits: torch.Tensor, history: torch.Tensor, repeat: torch.Tensor,

@@ -1,3 +1,3 @@
 """Architectures; importing the package registers them."""
-from . import lalepel, mekizen, pozozen, qwen2_moe  # noqa: F401
+from . import gugozen, lalepel, mekizen, pozozen, qwen2_moe  # noqa: F401
 from .model import Model, load_model  # noqa: F401

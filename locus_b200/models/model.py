@@ -74,11 +74,15 @@ class Model:
         return sorted(mods)
 
     def cache_needs(self) -> List[Tuple[Optional[PagedKvSpec], Optional[StateSpec], Optional[int]]]:
-        """For every entry of the run order: (paged spec, state spec, cache_of)."""
+        """For every entry of the run order: (paged spec, state spec, cache_of); behind them one more entry when the
+        embedding keeps something per request (its state lives in the requests' slots like a mixer's)."""
         out = []
         for call in self.plan.order:
             paged, state = self.blocks[call.layer].mixer.cache_needs()
             out.append((paged, state, call.cache_of))
+        state = self.embedding.state_needs() if hasattr(self.embedding, "state_needs") else None
+        if state is not None:
+            out.append((None, state, None))
         return out
 
     def param_bytes(self) -> int:
@@ -108,8 +112,11 @@ class Model:
         rt = self.rt
         T = batch.T
         x = rt.rows("model.x", self.plan.hidden_size * self.plan.residual_streams, torch.float32, T)
-        self.embedding.forward(batch.tokens, x)
         order = self.plan.order
+        if len(caches) > len(order):
+            self.embedding.forward(batch.tokens, x, batch=batch, cache=caches[len(order)])
+        else:
+            self.embedding.forward(batch.tokens, x)
         for i, (call, cache) in enumerate(zip(order, caches)):
             # a block may leave its last addition to the residual stream to the next block's first norm,
             # the last block to the final norm
@@ -133,9 +140,9 @@ def load_model(model_dir: str, dtype: torch.dtype, device="cuda:0") -> Model:
     from ..weights.safetensors_io import ModelFiles
 
     entry, cfg = load_config(model_dir)
-    model = Model(entry.build_plan(cfg), dtype, device)
     files = ModelFiles(model_dir)
     try:
+        model = Model(entry.plan(cfg, files), dtype, device)
         load_weights(model, files)
     finally:
         files.close()

@@ -3,5 +3,5 @@ from .base import (Arrangement, FeedForward, LayerCall, LayerSpec, Mixer, ModelP
                    Part, PartSpec, PositionEncoding, RotaryTable, StateSpec, StepPlan, TensorSource, iter_parts,
                    make_part, register_arrangement, register_embedding, register_feed_forward,
                    register_head, register_mixer, register_norm, register_position, registered)
-from . import (norm, position, attention, latent_attention, retention, mlstm, state_space, delta_rule, parallel,  # noqa: F401
+from . import (norm, position, attention, latent_attention, retention, mlstm, state_space, delta_rule, parallel, gla,  # noqa: F401
                feed_forward, block)  # noqa: F401  (registration)

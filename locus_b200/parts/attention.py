@@ -19,9 +19,11 @@ and contributes nothing to a score or an output.  The score's factor is then the
 
 Further forms, each an option of its own: a window that keeps a request's first ``keep_first`` tokens in sight (query i
 sees key j <= i if i - j < window or j < keep_first; kept tokens stay at their positions); a softmax with a ``sink`` (one
-more term of score 0 and no value in the denominator); a short causal convolution over time on every channel of q, k
+more term in the denominator that has no value: of score 0, or with ``sink`` "learned" of a score per query head that is
+a tensor of the layer and is not multiplied by the scores' factor); a short causal convolution over time on every channel of q, k
 and v directly behind the projection (``conv_taps``; the last taps - 1 projected rows of a request are its state); q
-and k divided by their root mean square per head behind the rotation (``qk_norm``); the heads' outputs multiplied by
+and k divided by their root mean square per head behind the rotation (``qk_norm`` "rms"), or an RMS norm with weights over
+the whole q and the whole k projection, all heads at once, in front of the rotation (``qk_norm`` "whole"); the heads' outputs multiplied by
 sigmoid(W_g h) in front of the output projection (``out_gate``); a layer without keys and values of its own
 (``has_kv`` off: it reads the cache of the layer call that the run order names).  With any of these (or ``shaped``)
 the projections are one product into float32 rows [q | k | v | gate] at the stored sizes, and one kernel
@@ -82,7 +84,8 @@ class AttentionTiles(StepPlan):
 # tensor names below an attention's prefix, by role; an architecture with other names passes its own
 NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
          "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias", "o_bias": "o_proj.bias",
-         "q_conv": "q_proj.conv", "k_conv": "k_proj.conv", "v_conv": "v_proj.conv", "gate": "g_proj.weight"}
+         "q_conv": "q_proj.conv", "k_conv": "k_proj.conv", "v_conv": "v_proj.conv", "gate": "g_proj.weight",
+         "sink": "sink", "q_norm": "q_norm.weight", "k_norm": "k_norm.weight"}
 
 
 class Attention(Mixer):
@@ -102,13 +105,18 @@ class Attention(Mixer):
         where that is more than its own window and kept tokens (another layer call reads them with a wider mask)."""
         super().__init__(prefix)
         self.keep_first, self.sink = (int(keep_first) if window else 0), bool(sink)
+        if sink not in (False, True, "learned"):
+            raise ValueError(f"attention: sink {sink!r} (known: False, True, 'learned')")
+        self.sink_learned = sink == "learned"
         self.conv_taps, self.qk_norm, self.qk_norm_eps = int(conv_taps), qk_norm, float(qk_norm_eps)
         self.out_gate, self.has_kv = bool(out_gate), bool(has_kv)
         self.shaped = bool(shaped or self.conv_taps > 0 or qk_norm or out_gate or not has_kv)
+        if qk_norm == "whole" and self.conv_taps > 0:
+            raise ValueError("attention: a norm over the whole projections does not go with a convolution behind them")
         if self.conv_taps > K.PREP_MAX_TAPS:
             raise ValueError(f"attention: a convolution over {conv_taps} tokens (at most {K.PREP_MAX_TAPS})")
-        if qk_norm not in (None, "rms", "unit"):
-            raise ValueError(f"attention: qk_norm {qk_norm!r} (known: rms, unit)")
+        if qk_norm not in (None, "rms", "unit", "whole"):
+            raise ValueError(f"attention: qk_norm {qk_norm!r} (known: rms, unit, whole)")
         self.cache_window = int(window if cache_window is None else cache_window)
         self.cache_keep = int(self.keep_first if cache_keep is None else cache_keep) if self.cache_window else 0
         if n_heads % n_kv_heads:
@@ -161,6 +169,7 @@ class Attention(Mixer):
             shapes["wo_stored" if self.head_dim != self.v_dim else "wo"] = (self.hidden, self.n_heads * self.v_dim)
             if self.o_bias:
                 shapes["bo"] = (self.hidden,)
+            shapes.update(self._extra_shapes())
             return shapes
         if self.padded and "wqkv" not in self.params:
             # loaded as stored, laid out for the kernels in bind
@@ -176,7 +185,24 @@ class Attention(Mixer):
                 shapes["bqkv"] = (self.q_dim + 2 * self.kv_dim,)
         if self.o_bias:
             shapes["bo"] = (self.hidden,)
+        shapes.update(self._extra_shapes())
         return shapes
+
+    def _extra_shapes(self):
+        """A learned sink per query head; the weights of a norm over the whole q and k projections."""
+        s = {}
+        if self.sink_learned:
+            s["sink"] = (self.n_heads,)
+        if self.qk_norm == "whole":
+            s["q_norm"] = (self.n_heads * self.qk_dim,)
+            if self.has_kv:
+                s["k_norm"] = (self.n_kv_heads * self.qk_dim,)
+        return s
+
+    def _extra_sources(self):
+        p, nm = self.prefix, self.names
+        kinds = {"sink": "bias", "q_norm": "norm", "k_norm": "norm"}
+        return [TensorSource(f"{p}.{nm[name]}", shape, name, 0, kinds[name]) for name, shape in self._extra_shapes().items()]
 
     def sources(self):
         p, nm = self.prefix, self.names
@@ -192,7 +218,7 @@ class Attention(Mixer):
                                     "wo_stored" if self.head_dim != self.v_dim else "wo"))
             if self.o_bias:
                 out.append(TensorSource(f"{p}.{nm['o_bias']}", (self.hidden,), "bo", 0, "bias"))
-            return out
+            return out + self._extra_sources()
         if self.padded:
             out = [TensorSource(f"{p}.{nm[r]}", (n, self.hidden), f"w{r}_stored") for r, n in self._stored()]
             if self.qkv_bias:
@@ -206,10 +232,12 @@ class Attention(Mixer):
             out.append(TensorSource(f"{p}.{nm['o']}", (self.hidden, self.q_dim), "wo"))
         if self.o_bias:
             out.append(TensorSource(f"{p}.{nm['o_bias']}", (self.hidden,), "bo", 0, "bias"))
-        return out
+        return out + self._extra_sources()
 
     def bind(self, rt) -> None:
         self._scale = None
+        # what the kernels get as the sink: a flag, or the learned scores as float32
+        self._sink_arg = self.params["sink"].float().contiguous() if self.sink_learned else self.sink
         if self.out_scale != 1.0:
             self._scale = rt.shared_object(("row_scale", self.out_scale), lambda: torch.full(
                 (rt.max_tokens,), self.out_scale, dtype=torch.float32, device=rt.device))
@@ -277,13 +305,19 @@ class Attention(Mixer):
         q = rt.rows("attention.q", self.q_dim, rt.dtype, T)
         kv = self.n_kv_heads if self.has_kv else 0
         D = self.head_dim
+        if self.qk_norm == "whole":
+            spans = [(self.in_rows[0][1], self.in_rows[0][2], self.params["q_norm"])]
+            if kv:
+                spans.append((self.in_rows[1][1], self.in_rows[1][2], self.params["k_norm"]))
+            K.span_rmsnorm(proj, spans, self.qk_norm_eps)
         K.head_prep(proj, offsets=[r[1] for r in self.in_rows[:3]], heads=(self.n_heads, kv, kv),
                     dims=(self.qk_dim, self.qk_dim, self.v_dim), laid=(D, D, D), state_slots=batch.state_slots,
                     seg_q0=batch.seg_q0, seg_qn=batch.seg_qn, n_seg=batch.n_seg,
                     longest_new=max(batch.host_seg_qn) if batch.host_seg_qn else T, positions=batch.positions, q_out=q,
                     pool=cache.pool if kv else None, slots=gb.slots if kv else None, page_tokens=gb.page_tokens,
                     write_kv=cache.writes, conv=self.params.get("conv"), state=cache.state if self.conv_taps > 1 else None,
-                    inv_freq=table.inv_freq if table else None, rot=table.rot_dim if table else 0, norm=self.qk_norm,
+                    inv_freq=table.inv_freq if table else None, rot=table.rot_dim if table else 0,
+                    norm=None if self.qk_norm == "whole" else self.qk_norm,
                     eps=self.qk_norm_eps)
         o = rt.rows("attention.o", self.q_dim, rt.dtype, T)
         self._attend(q, o, batch, cache, gb, rt)
@@ -320,7 +354,7 @@ class Attention(Mixer):
         """o = attention of the step's queries ``q`` over the layer's pages, by the kernels that fit the step."""
         T = batch.T
         special = bool(self.keep_first or self.sink)
-        extra = dict(keep_first=self.keep_first, sink=self.sink) if special else {}
+        extra = dict(keep_first=self.keep_first, sink=self._sink_arg) if special else {}
         common = dict(seg_q0=batch.seg_q0, seg_qn=batch.seg_qn, seg_ctx=batch.seg_ctx,
                       block_table=gb.block_table, n_heads=self.n_heads, n_kv_heads=self.n_kv_heads,
                       head_dim=self.head_dim, page_tokens=gb.page_tokens, window=self.window,

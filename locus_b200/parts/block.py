@@ -10,16 +10,22 @@ norms sit on what they give.
 ``StreamedPreNorm``: pre-norm sublayers over several copies of the residual stream that are read as a weighted sum
 and mixed among themselves at every write-back (below).
 
-``Embedding``: x = table[token] (llama.cpp:450).  ``LmHead``: logits = W . h in float32,
+``PostNorm``: x <- norm1(alpha x + mixer(x)); x <- norm2(alpha x + feed_forward(x)): the sublayers read x itself and the
+norm sits on the sum.
+
+``Embedding``: x = table[token] (llama.cpp:450); optionally plus a row of a second table addressed by a hash of the
+previous and the current token.  ``LmHead``: logits = W . h in float32,
 W being the embedding table when the head is tied (llama.cpp:292-297, 512-513): the head then
 names the embedding's tensor as the source of its weight.
 """
 from __future__ import annotations
 
+from typing import Optional
+
 import torch
 
 from .. import kernels as K
-from .base import (Arrangement, Part, PartSpec, TensorSource, make_part, register_arrangement,
+from .base import (Arrangement, Part, PartSpec, StateSpec, TensorSource, make_part, register_arrangement,
                    register_embedding, register_head)
 
 
@@ -110,6 +116,63 @@ class OutputNorm(Arrangement):
             y.zero_()
             self.ff.forward(h, batch, y, rt)
         self.norm2.forward_add(y, x)
+
+
+class PostNorm(Arrangement):
+    """The norm behind the sum: x <- norm1(alpha x + mixer(x)); x <- norm2(alpha x + feed_forward(x)), with a layer norm
+    (weight and bias) whose statistics, like the sum and the residual stream, are float32.  The sublayers read x itself
+    (in a bfloat16 model its rounding, which the norm's own pass writes beside the float32 row) and write float32 rows.
+    ``feed_forward`` may be absent (kind "none"): the layer is then its mixer and the first norm alone."""
+
+    def __init__(self, prefix: str, *, hidden: int, norm: PartSpec, mixer: PartSpec, feed_forward: PartSpec,
+                 alpha: float = 1.0, mixer_prefix: str = "mix", ff_prefix: str = "mlp", norm1_name: str = "norm1",
+                 norm2_name: str = "norm2", bias_suffix: str = ".b") -> None:
+        super().__init__(prefix)
+        self.hidden, self.alpha = int(hidden), float(alpha)
+        if norm.kind != "layernorm":
+            raise ValueError(f"post_norm: the norm behind the sum is a layer norm, got {norm.kind!r}")
+
+        def norm_part(name):
+            spec = PartSpec(norm.kind, {**norm.args, "tensor": f"{prefix}.{name}", "bias_tensor": f"{prefix}.{name}{bias_suffix}"})
+            return make_part("norm", spec, f"{prefix}.{name}")
+
+        self.norm1 = norm_part(norm1_name)
+        self.mixer = make_part("mixer", mixer, f"{prefix}.{mixer_prefix}")
+        self.ff = None if feed_forward.kind == "none" else make_part("feed_forward", feed_forward, f"{prefix}.{ff_prefix}")
+        self.norm2 = norm_part(norm2_name) if self.ff is not None else None
+
+    def sub_parts(self):
+        return [self.norm1, self.mixer] + ([self.norm2, self.ff] if self.ff is not None else [])
+
+    def kernel_modules(self, dtype):
+        return ["elementwise"]
+
+    def forward(self, x, batch, cache, rt) -> None:
+        T = batch.T
+        rt.defer_add = False   # what a sublayer gives is summed and normed here, at once: nothing may be left pending
+        y = rt.rows("block.y", self.hidden, torch.float32, T)
+        # what the sublayers read: x itself; in a bfloat16 model the copy that the norm in front wrote (the first
+        # layer's first sublayer makes its own)
+        low = rt.dtype != torch.float32
+        h = rt.rows("block.h", self.hidden, rt.dtype, T) if low else x
+        if low and getattr(rt, "_post_norm_rows", None) is not x:
+            K.cast_rows(x, h)
+        rt._post_norm_rows = None
+        if self.mixer.can_overwrite:
+            self.mixer.forward(h, batch, cache, y, rt, accumulate=False)
+        else:
+            y.zero_()
+            self.mixer.forward(h, batch, cache, y, rt)
+        self.norm1.forward_post(x, y, self.alpha, cast=h if low else None)
+        if self.ff is not None:
+            if self.ff.can_overwrite:
+                self.ff.forward(h, batch, y, rt, accumulate=False)
+            else:
+                y.zero_()
+                self.ff.forward(h, batch, y, rt)
+            self.norm2.forward_post(x, y, self.alpha, cast=h if low else None)
+        if low:
+            rt._post_norm_rows = x   # block.h holds x's rounding for the block behind this one
 
 
 class StreamedPreNorm(Arrangement):
@@ -210,24 +273,51 @@ class StreamedPreNorm(Arrangement):
 
 class Embedding(Part):
     def __init__(self, prefix: str, *, vocab: int, hidden: int, tensor: str = "", copies: int = 1,
-                 scale: float = 1.0) -> None:
+                 scale: float = 1.0, pair: Optional[dict] = None) -> None:
         """``tensor``: the checkpoint tensor's name where it is not ``<prefix>.weight``.  ``copies`` > 1: a row of the
         output holds the embedding that many times (a model with several copies of the residual stream).  ``scale``:
-        a factor on the embedding, applied in float32."""
+        a factor on the embedding, applied in float32.  ``pair`` = {tensor, buckets, mul_prev, mul_cur}: a second table
+        of buckets + 1 rows whose row (previous token * mul_prev + token * mul_cur) mod buckets is added (its last row for
+        a request's first token).  The token that a request's last step ended on is kept in the request's state slot
+        (``state_needs``), so that a prompt may be cut anywhere."""
         super().__init__(prefix)
         self.vocab, self.hidden, self.copies, self.scale = int(vocab), int(hidden), int(copies), float(scale)
         self.tensor = str(tensor or prefix + ".weight")
+        self.pair = dict(pair) if pair else None
+        if self.pair is not None:
+            if self.copies != 1 or self.scale != 1.0:
+                raise ValueError("embedding: the pair table goes with one copy and no factor")
+            if int(self.pair["buckets"]) <= 0 or int(self.pair["mul_prev"]) < 0 or int(self.pair["mul_cur"]) < 0:
+                raise ValueError("embedding: the pair table needs positive buckets and multipliers that are not negative")
 
     def param_shapes(self):
-        return {"table": (self.vocab, self.hidden)}
+        s = {"table": (self.vocab, self.hidden)}
+        if self.pair is not None:
+            s["pair"] = (int(self.pair["buckets"]) + 1, self.hidden)
+        return s
 
     def sources(self):
-        return [TensorSource(self.tensor, (self.vocab, self.hidden), "table")]
+        out = [TensorSource(self.tensor, (self.vocab, self.hidden), "table")]
+        if self.pair is not None:
+            out.append(TensorSource(str(self.pair["tensor"]), (int(self.pair["buckets"]) + 1, self.hidden), "pair"))
+        return out
 
     def kernel_modules(self, dtype):
         return ["elementwise"]
 
-    def forward(self, tokens: torch.Tensor, out: torch.Tensor) -> None:
+    def state_needs(self) -> Optional[StateSpec]:
+        """What the embedding keeps per request: the last token it saw, when it has a pair table."""
+        return StateSpec((1,), torch.int32) if self.pair is not None else None
+
+    def forward(self, tokens: torch.Tensor, out: torch.Tensor, batch=None, cache=None) -> None:
+        if self.pair is not None:
+            if batch is None or cache is None or cache.state is None:
+                raise ValueError("embedding: a pair table needs the step's segments and the requests' state slots")
+            K.embed_pair(tokens, batch.positions, self.params["table"], self.params["pair"], out, seg_q0=batch.seg_q0,
+                         seg_qn=batch.seg_qn, state_slots=batch.state_slots, last=cache.state, n_seg=batch.n_seg,
+                         longest_new=max(batch.host_seg_qn) if batch.host_seg_qn else batch.T,
+                         mul_prev=int(self.pair["mul_prev"]), mul_cur=int(self.pair["mul_cur"]))
+            return
         if self.copies > 1 or self.scale != 1.0:
             K.embed_rows(tokens, self.params["table"], out, copies=self.copies, scale=self.scale)
         else:
@@ -259,5 +349,6 @@ class LmHead(Part):
 register_arrangement("pre_norm", PreNorm)
 register_arrangement("output_norm", OutputNorm)
 register_arrangement("streamed_pre_norm", StreamedPreNorm)
+register_arrangement("post_norm", PostNorm)
 register_embedding("embedding", Embedding)
 register_head("linear", LmHead)

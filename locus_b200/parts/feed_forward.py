@@ -11,6 +11,14 @@ Sparse (``moe_ffn`` llama.cpp:992-1077, ``moe_select`` llama.cpp:900-980):
     order, of w_e * SwiGLU_e(h); then the shared expert, scaled by
     sigmoid(w_shared_gate . h) when it is gated (llama.cpp:1062-1076), is added.
 
+Further forms: ``activation`` "relu2" (down(max(up h, 0)^2), no gate matrix) and "glu_clamp", a clamped gated unit
+
+    g = min(W_gate h, limit),  u = clamp(W_up h, -limit, limit),  out = W_down (g sigmoid(1.702 g) (u + 1)),
+
+whose two first products are one product against the stacked weight [gate | up] with a float32 result; and
+``weight_on_input``: a picked expert's weight multiplies its input, out = sum expert_e(w_e h), not its output (the two
+first products carry the weight as a factor, so it enters in front of the clamps).
+
 The batched form lays the (token, slot) pairs out by expert, runs each expert over its
 tokens, and sums each token's pairs in slot order without atomics (the reference's
 ``moe_ffn_batch``, llama.cpp:1079-1235, does the same to stay byte-identical).
@@ -25,25 +33,30 @@ from .. import kernels as K
 from .base import FeedForward, PendingAdd, TensorSource, register_feed_forward
 
 
-ACTIVATIONS = ("swiglu", "relu2")
+ACTIVATIONS = ("swiglu", "relu2", "glu_clamp")
 # tensor names below a feed-forward's prefix, by role; an architecture with other names passes its own
 DENSE_NAMES = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}
 
 
 class DenseMlp(FeedForward):
-    """``activation`` "swiglu": down(silu(gate h) * (up h)); "relu2": down(max(up h, 0)^2), no gate matrix."""
+    """``activation`` "swiglu": down(silu(gate h) * (up h)); "relu2": down(max(up h, 0)^2), no gate matrix; "glu_clamp":
+    the clamped gated unit of the head of the file with its ``limit``."""
 
     can_overwrite = True
 
     def __init__(self, prefix: str, *, hidden: int, intermediate: int, activation: str = "swiglu",
-                 names: Optional[dict] = None) -> None:
+                 names: Optional[dict] = None, limit: float = 0.0) -> None:
         super().__init__(prefix)
         if activation not in ACTIVATIONS:
             raise ValueError(f"dense_mlp: activation {activation!r} (known: {', '.join(ACTIVATIONS)})")
-        self.hidden, self.inter, self.activation = int(hidden), int(intermediate), activation
+        self.hidden, self.inter, self.activation, self.limit = int(hidden), int(intermediate), activation, float(limit)
+        if activation == "glu_clamp" and not self.limit > 0:
+            raise ValueError(f"dense_mlp: a clamped gated unit needs a positive limit, got {limit}")
         self.names = {**DENSE_NAMES, **(names or {})}
 
     def param_shapes(self):
+        if self.activation == "glu_clamp":
+            return {"w_gate_up": (2 * self.inter, self.hidden), "w_down": (self.hidden, self.inter)}
         s = {"w_up": (self.inter, self.hidden), "w_down": (self.hidden, self.inter)}
         if self.activation == "swiglu":
             s["w_gate"] = (self.inter, self.hidden)
@@ -51,6 +64,10 @@ class DenseMlp(FeedForward):
 
     def sources(self):
         p, n = self.prefix, self.names
+        if self.activation == "glu_clamp":
+            return [TensorSource(f"{p}.{n['gate']}", (self.inter, self.hidden), "w_gate_up", 0),
+                    TensorSource(f"{p}.{n['up']}", (self.inter, self.hidden), "w_gate_up", self.inter),
+                    TensorSource(f"{p}.{n['down']}", (self.hidden, self.inter), "w_down")]
         out = [TensorSource(f"{p}.{n['up']}", (self.inter, self.hidden), "w_up"),
                TensorSource(f"{p}.{n['down']}", (self.hidden, self.inter), "w_down")]
         if self.activation == "swiglu":
@@ -58,7 +75,7 @@ class DenseMlp(FeedForward):
         return out
 
     def kernel_modules(self, dtype):
-        return ["gemm_simt", "gemv"] + (["gemm_skinny", "gemm_tc"] if dtype == torch.bfloat16 else [])
+        return ["gemm_simt", "gemv", "elementwise"] + (["gemm_skinny", "gemm_tc"] if dtype == torch.bfloat16 else [])
 
     def forward(self, h, batch, residual, rt, row_scale=None, accumulate=True) -> None:
         self.forward_down(self.forward_up(h, rt), residual, rt, row_scale, accumulate)
@@ -69,6 +86,10 @@ class DenseMlp(FeedForward):
         act = rt.rows(f"dense_mlp.act{self.inter}", self.inter, rt.dtype, h.shape[0])
         if self.activation == "swiglu":
             K.linear(h, self.params["w_gate"], act, w2=self.params["w_up"])
+        elif self.activation == "glu_clamp":
+            gu = rt.rows(f"dense_mlp.gu{2 * self.inter}", 2 * self.inter, torch.float32, h.shape[0])
+            K.linear(h, self.params["w_gate_up"], gu)
+            K.glu_clamp(gu, self.limit, act)
         else:
             K.linear(h, self.params["w_up"], act, act="relu2")
         return act
@@ -103,7 +124,8 @@ class SparseMoe(FeedForward):
                  weight_scale: float = 1.0, score_fn: str = "softmax", selection_bias: bool = False,
                  n_group: int = 1, n_group_used: int = 1, activation: str = "swiglu", router_bias: bool = False,
                  names: Optional[dict] = None, shared_names: Optional[dict] = None, n_identity: int = 0,
-                 group_score: str = "top2") -> None:
+                 group_score: str = "top2", limit: float = 0.0, shared_limit: Optional[float] = None,
+                 weight_on_input: bool = False) -> None:
         """``router_bias``: the router has a bias [n_experts] that is part of its logits (selection and weights
         alike; with softmax scores and ``norm_topk`` the weights are then the softmax over the picked logits).
         ``names`` / ``shared_names``: tensor names where they differ from ``MOE_NAMES`` / ``DENSE_NAMES``.
@@ -114,8 +136,14 @@ class SparseMoe(FeedForward):
         is judged by, "top2" (the sum of its two best selection scores) or "best" (its best one).
         ``n_identity``: the router has that many outputs more than there are experts with weights; they stand for
         experts whose output is their input (times the weight).  Scores, selection bias, groups and top-k run over
-        all ``n_experts + n_identity`` router outputs."""
+        all ``n_experts + n_identity`` router outputs.  ``limit`` / ``shared_limit``: the clamps of "glu_clamp" experts
+        and of the shared one (default: the experts').  ``weight_on_input``: see the head of the file ("glu_clamp" only)."""
         super().__init__(prefix)
+        self.limit, self.weight_on_input = float(limit), bool(weight_on_input)
+        if activation == "glu_clamp" and not self.limit > 0:
+            raise ValueError(f"sparse_moe: clamped gated experts need a positive limit, got {limit}")
+        if self.weight_on_input and (activation != "glu_clamp" or n_identity):
+            raise ValueError("sparse_moe: the weight on an expert's input goes with glu_clamp experts and no identity experts")
         self.n_identity = int(n_identity)
         if self.n_identity < 0:
             raise ValueError(f"sparse_moe: {n_identity} identity experts")
@@ -140,7 +168,8 @@ class SparseMoe(FeedForward):
         self.activation, self.has_router_bias = activation, bool(router_bias)
         self.names = {**MOE_NAMES, **(names or {})}
         self.shared = (DenseMlp(f"{prefix}.{self.names['shared']}", hidden=hidden, intermediate=self.Is,
-                                activation=activation, names=shared_names)
+                                activation=activation, names=shared_names,
+                                limit=self.limit if shared_limit is None else float(shared_limit))
                        if self.Is > 0 else None)
         self._layout = None
         self._scratch = None
@@ -155,9 +184,12 @@ class SparseMoe(FeedForward):
     def param_shapes(self):
         s = {
             "router": (self.R, self.hidden),
-            "up_exps": (self.E, self.I, self.hidden),
             "down_exps": (self.E, self.hidden, self.I),
         }
+        if self.activation == "glu_clamp":
+            s["gate_up_exps"] = (self.E, 2 * self.I, self.hidden)
+        else:
+            s["up_exps"] = (self.E, self.I, self.hidden)
         if self.activation == "swiglu":
             s["gate_exps"] = (self.E, self.I, self.hidden)
         if self.has_router_bias:
@@ -174,6 +206,11 @@ class SparseMoe(FeedForward):
         for e in range(self.E):
             if self.activation == "swiglu":
                 out.append(TensorSource(f"{p}.{n['expert_gate'].format(e=e)}", (self.I, self.hidden), "gate_exps", e * self.I))
+            if self.activation == "glu_clamp":
+                out.append(TensorSource(f"{p}.{n['expert_gate'].format(e=e)}", (self.I, self.hidden), "gate_up_exps", 2 * e * self.I))
+                out.append(TensorSource(f"{p}.{n['expert_up'].format(e=e)}", (self.I, self.hidden), "gate_up_exps", (2 * e + 1) * self.I))
+                out.append(TensorSource(f"{p}.{n['expert_down'].format(e=e)}", (self.hidden, self.I), "down_exps", e * self.hidden))
+                continue
             out.append(TensorSource(f"{p}.{n['expert_up'].format(e=e)}", (self.I, self.hidden), "up_exps", e * self.I))
             out.append(TensorSource(f"{p}.{n['expert_down'].format(e=e)}", (self.hidden, self.I), "down_exps",
                                     e * self.hidden))
@@ -216,9 +253,16 @@ class SparseMoe(FeedForward):
             # router rows and the gate row as one matrix (a copy of a few hundred KB)
             self._router_all = torch.cat([r, g.view(1, -1)], 0).contiguous() if g is not None else r
 
-    def _first_product(self, x, act, **kw) -> None:
+    def _first_product(self, x, act, rt=None, scale=None, **kw) -> None:
+        """``scale`` = (weights, the pairs' order): the picks' weights as a factor on the experts' input."""
         if self.activation == "swiglu":
             K.linear(x, self.params["gate_exps"], act, w2=self.params["up_exps"], **kw)
+        elif self.activation == "glu_clamp":
+            n = kw["n_rows"]
+            gu = rt.rows(f"moe.gu{2 * self.I}", 2 * self.I, torch.float32, n, per_token=self.k)
+            K.linear(x, self.params["gate_up_exps"], gu, **kw)
+            K.glu_clamp(gu, self.limit, act, n_rows=n, row_scale=scale[0] if scale else None,
+                        scale_rows=scale[1] if scale else None)
         else:
             K.linear(x, self.params["up_exps"], act, act="relu2", **kw)
 
@@ -234,7 +278,9 @@ class SparseMoe(FeedForward):
         # which kernels the expert products run on decides the row tile of the expert layout
         tile = K.FEW_ROWS if T <= K.FEW_ROWS else K.expert_tile(n_pairs, self.E)
         widths_ok = self.I % 8 == 0 and self.hidden % 8 == 0
-        all_bf16 = (K.tensor_cores_take(h, self.params["up_exps"]) and widths_ok
+        first_w = self.params["gate_up_exps" if self.activation == "glu_clamp" else "up_exps"]
+        on_input = (wts, lay.sorted_pair) if self.weight_on_input else None
+        all_bf16 = (K.tensor_cores_take(h, first_w) and widths_ok
                     and self.params["down_exps"].dtype == torch.bfloat16)
         if not all_bf16 and widths_ok and n_pairs <= K.FEW_ROWS * self.E:
             # No tensor-core form (float32) and a handful of rows per expert: tiles of 8 rows on the row-streaming
@@ -298,14 +344,16 @@ class SparseMoe(FeedForward):
             K.moe_identity(h, wts, lay, pair_out, n_pairs=n_pairs, top_k=self.k, n_real=self.E)
         if streamed or not all_bf16:
             # few rows per expert (or no tensor-core form): the kernels gather the token rows themselves
-            self._first_product(h, act, x_rows=lay.sorted_pair, x_row_div=self.k, layout=lay, n_rows=n_pairs)
+            self._first_product(h, act, rt=rt, scale=on_input, x_rows=lay.sorted_pair, x_row_div=self.k, layout=lay,
+                                n_rows=n_pairs)
         else:
             # tcgen05 kernel: TMA reads whole row ranges, so lay the tokens out in expert order first
             xs = rt.rows("moe.x_sorted", self.hidden, rt.dtype, n_pairs, per_token=self.k)
             K.gather_rows(h, lay.sorted_pair, self.k, xs, n_pairs)
-            self._first_product(xs, act, layout=lay, n_rows=n_pairs)
-        K.linear(act, self.params["down_exps"], pair_out, layout=lay, n_rows=n_pairs, row_scale=wts,
-                 scale_rows=lay.sorted_pair, lists_ready=True, second_tiles=True)
+            self._first_product(xs, act, rt=rt, scale=on_input, layout=lay, n_rows=n_pairs)
+        K.linear(act, self.params["down_exps"], pair_out, layout=lay, n_rows=n_pairs,
+                 row_scale=None if self.weight_on_input else wts,
+                 scale_rows=None if self.weight_on_input else lay.sorted_pair, lists_ready=True, second_tiles=True)
         if overlap:
             rt.join()
         if self.shared is not None and not overlap:

@@ -15,6 +15,12 @@ are never expanded per key: W_uk is applied to the query instead (q_abs = W_uk^T
 the cached rows as they are, and W_uv is applied to the attention's output (sum_j p_j c_j).  The two per-head
 products are grouped products (the heads in the place of experts) over head-major rows [head][token].
 
+Options: ``q_rank`` 0: no query latent, q = W_q h directly.  ``out_gate``: the concatenated heads' outputs are
+multiplied by sigmoid(W_g h) in front of the output projection.  ``has_kv`` off: the layer has no W_dkv; it reads the
+cache rows of the layer call that the run order names (that layer's latent and rotated key part as cached) with its own
+W_uk, W_uv and queries.  The rotated parts' pairs are interleaved, (2i, 2i + 1), or the halves (i, i + dims/2), as the
+position encoding says.
+
 The softmax's denominator may hold a learned sink per head, exp(sink_h), without a key or a value.  A query at
 position p sees the keys j with p - window < j <= p (window 0: all).  Scores, softmax, the norms' statistics,
 positions and angles are float32 (angles are formed in float64 and rounded once).
@@ -89,7 +95,8 @@ class LatentAttention(Mixer):
 
     def __init__(self, prefix: str, *, hidden: int, n_heads: int, nope_dim: int, rot_dim: int, v_dim: int,
                  q_rank: int, kv_rank: int, scale: float, eps: float, window: int = 0, sink: bool = False,
-                 position: PartSpec = PartSpec("none"), names: Optional[dict] = None) -> None:
+                 position: PartSpec = PartSpec("none"), names: Optional[dict] = None, out_gate: bool = False,
+                 has_kv: bool = True) -> None:
         """``position``: the encoding of the rotated parts (a "rotary" spec over ``rot_dim`` with interleaved
         pairs, or "none").  ``names``: tensor names below the prefix where they differ from the defaults."""
         super().__init__(prefix)
@@ -99,10 +106,17 @@ class LatentAttention(Mixer):
         self.hidden, self.H, self.dn, self.dr, self.dv = int(hidden), int(n_heads), int(nope_dim), int(rot_dim), int(v_dim)
         self.q_rank, self.kv_rank, self.scale, self.eps = int(q_rank), int(kv_rank), float(scale), float(eps)
         self.window, self.has_sink = int(window), bool(sink)
+        self.out_gate, self.has_kv = bool(out_gate), bool(has_kv)
+        if self.q_rank < 0:
+            raise ValueError(f"latent_attention: q_rank {q_rank}")
         self.position = make_part("position", position, prefix + ".position")
         self.names = {"dq": "dq", "dq_norm": "dq.norm", "uq": "uq", "dkv": "dkv", "dkv_norm": "dkv.norm", "uk": "uk",
-                      "uv": "uv", "sink": "sink", "o": "o", **(names or {})}
+                      "uv": "uv", "sink": "sink", "o": "o", "q": "q", "gate": "g", **(names or {})}
         self.row = self.kv_rank + self.dr
+        # the product whose result stays float32: [query latent | key/value latent and shared key part | gate]
+        self.n_down = self.q_rank + (self.row if self.has_kv else 0)
+        self.n_gate = self.H * self.dv if self.out_gate else 0
+        self.down_width = -(-(self.n_down + self.n_gate) // 8) * 8
         # whether the per-head products may run on the kernels that want rows of whole 16-byte pieces
         self.widths_ok = self.dn % 8 == 0 and self.kv_rank % 8 == 0
 
@@ -111,21 +125,33 @@ class LatentAttention(Mixer):
 
     # -- weights ------------------------------------------------------------
     def param_shapes(self):
-        s = {"w_down": (self.q_rank + self.row, self.hidden), "g_q": (self.q_rank,), "g_kv": (self.kv_rank,),
-             "w_uq": (self.H * (self.dn + self.dr), self.q_rank), "w_uk": (self.H * self.dn, self.kv_rank),
+        s = {"w_uq": (self.H * (self.dn + self.dr), self.q_rank or self.hidden), "w_uk": (self.H * self.dn, self.kv_rank),
              "w_uv": (self.H * self.dv, self.kv_rank), "w_o": (self.hidden, self.H * self.dv)}
+        if self.n_down + self.n_gate:
+            s["w_down"] = (self.down_width, self.hidden)
+        if self.q_rank:
+            s["g_q"] = (self.q_rank,)
+        if self.has_kv:
+            s["g_kv"] = (self.kv_rank,)
         if self.has_sink:
             s["sink"] = (self.H,)
         return s
 
     def sources(self):
         p, n = self.prefix, self.names
-        out = [TensorSource(f"{p}.{n['dq']}", (self.q_rank, self.hidden), "w_down", 0),
-               TensorSource(f"{p}.{n['dkv']}", (self.row, self.hidden), "w_down", self.q_rank),
-               TensorSource(f"{p}.{n['dq_norm']}", (self.q_rank,), "g_q", 0, "norm"),
-               TensorSource(f"{p}.{n['dkv_norm']}", (self.kv_rank,), "g_kv", 0, "norm"),
-               TensorSource(f"{p}.{n['uq']}", (self.H * (self.dn + self.dr), self.q_rank), "w_uq"),
-               TensorSource(f"{p}.{n['uk']}", (self.H * self.dn, self.kv_rank), "w_uk"),
+        out = []
+        if self.q_rank:
+            out += [TensorSource(f"{p}.{n['dq']}", (self.q_rank, self.hidden), "w_down", 0),
+                    TensorSource(f"{p}.{n['dq_norm']}", (self.q_rank,), "g_q", 0, "norm"),
+                    TensorSource(f"{p}.{n['uq']}", (self.H * (self.dn + self.dr), self.q_rank), "w_uq")]
+        else:
+            out.append(TensorSource(f"{p}.{n['q']}", (self.H * (self.dn + self.dr), self.hidden), "w_uq"))
+        if self.has_kv:
+            out += [TensorSource(f"{p}.{n['dkv']}", (self.row, self.hidden), "w_down", self.q_rank),
+                    TensorSource(f"{p}.{n['dkv_norm']}", (self.kv_rank,), "g_kv", 0, "norm")]
+        if self.out_gate:
+            out.append(TensorSource(f"{p}.{n['gate']}", (self.n_gate, self.hidden), "w_down", self.n_down))
+        out += [TensorSource(f"{p}.{n['uk']}", (self.H * self.dn, self.kv_rank), "w_uk"),
                TensorSource(f"{p}.{n['uv']}", (self.H * self.dv, self.kv_rank), "w_uv"),
                TensorSource(f"{p}.{n['o']}", (self.hidden, self.H * self.dv), "w_o")]
         if self.has_sink:
@@ -133,7 +159,7 @@ class LatentAttention(Mixer):
         return out
 
     def kernel_modules(self, dtype):
-        return ["elementwise", "gemm_simt", "gemv", "latent_attention"] + (
+        return ["elementwise", "gemm_simt", "gemv", "latent_attention"] + (["short_conv"] if self.out_gate else []) + (
             ["gemm_skinny", "gemm_tc"] if dtype == torch.bfloat16 else [])
 
     def cache_needs(self):
@@ -165,7 +191,9 @@ class LatentAttention(Mixer):
         self._w_uk_t = self.params["w_uk"].view(self.H, self.dn, self.kv_rank).transpose(1, 2).contiguous()
         self._w_uv = self.params["w_uv"].view(self.H, self.dv, self.kv_rank)
         self._sink = self.params["sink"].float().contiguous() if self.has_sink else None
-        self._gq, self._gkv = self.params["g_q"], self.params["g_kv"]
+        self._gq, self._gkv = self.params.get("g_q"), self.params.get("g_kv")
+        if "w_down" in self.params:
+            self.params["w_down"][self.n_down + self.n_gate:].zero_()
         self._tiles_key = self._query_tiles.key   # also settles which attention kernel this mixer runs
 
     # -- forward ------------------------------------------------------------
@@ -176,18 +204,25 @@ class LatentAttention(Mixer):
         freq = table.freq64 if table is not None else None
         pairs = table.rot_dim // 2 if table is not None else 0
         mag = table.magnitude if table is not None else 1.0
-        # both down-projections as one product, kept in float32 for the norms
-        dqkv = rt.rows("latent.dqkv", self.q_rank + self.row, torch.float32, T)
-        K.linear(h, self.params["w_down"], dqkv)
-        cq = rt.rows("latent.cq", self.q_rank, rt.dtype, T)
-        K.latent_prep(dqkv, batch.positions, freq, mag, self._gq, self._gkv, self.eps, cq, cache.pool, gb.slots,
-                      q_rank=self.q_rank, kv_rank=self.kv_rank, rot_dim=self.dr, rot_pairs=pairs, write=cache.writes)
+        half = table is not None and not table.interleaved
+        if not self.has_kv and cache.writes:
+            raise ValueError("latent_attention: a layer without a latent of its own must read another call's cache")
+        # the down-projections (and the gate's) as one product, kept in float32 for the norms and the sigmoid
+        down = None
+        if self.n_down + self.n_gate:
+            down = rt.rows(f"latent.down{self.down_width}", self.down_width, torch.float32, T)
+            K.linear(h, self.params["w_down"], down)
+        cq = rt.rows("latent.cq", self.q_rank, rt.dtype, T) if self.q_rank else None
+        if self.n_down:
+            K.latent_prep(down[:, :self.n_down], batch.positions, freq, mag,
+                          self._gq, self._gkv, self.eps, cq, cache.pool, gb.slots, q_rank=self.q_rank, kv_rank=self.kv_rank,
+                          rot_dim=self.dr, rot_pairs=pairs, write=cache.writes and self.has_kv, half_split=half)
         q = rt.rows("latent.q", H * (self.dn + self.dr), rt.dtype, T)
-        K.linear(cq, self.params["w_uq"], q)
+        K.linear(cq if self.q_rank else h, self.params["w_uq"], q)
         q_nope = rt.rows(f"latent.q_nope{self.dn}", self.dn, rt.dtype, H * T, per_token=H)
         q_rot = rt.rows("latent.q_rot", H * self.dr, rt.dtype, T)
         K.latent_q_split(q, batch.positions, freq, mag, q_nope, q_rot, n_heads=H, nope_dim=self.dn, rot_dim=self.dr,
-                         rot_pairs=pairs)
+                         rot_pairs=pairs, half_split=half)
         ht = batch.plans[self._head_tiles.key]
         lay = K.HeadLayout(H, ht["tile"], ht["offsets"], ht["tile_head"], ht["tile_row0"], ht["tile_rows"],
                            ht["n_tiles"], ht["count"])
@@ -218,6 +253,8 @@ class LatentAttention(Mixer):
         K.linear(o_lat, self._w_uv, o_hm, layout=lay, n_rows=H * T, lists_ready=True)
         o = rt.rows("latent.o", H * self.dv, rt.dtype, T)
         K.heads_to_rows(o_hm, o, n_tokens=T, n_heads=H)
+        if self.out_gate:
+            K.gate_rows(o, down, self.n_down, n_heads=H, dim=self.dv, laid=self.dv)
         K.linear(o, self.params["w_o"], residual, accumulate=accumulate)
 
 

@@ -83,6 +83,13 @@ class LayerNorm(Norm):
             add.apply(x)   # nothing is folded into this norm's pass
         K.layernorm(x, self.params["weight"], self.params["bias"], self.eps, out, rows, n_streams=self.streams, coef=coef)
 
+    def forward_post(self, x: torch.Tensor, y: torch.Tensor, alpha: float, cast: Optional[torch.Tensor] = None) -> None:
+        """x <- norm(alpha x + y) in place on the float32 residual stream (the norm behind a sublayer's sum); ``cast``:
+        the new rows once more in that buffer's element type."""
+        if self.streams != 1:
+            raise ValueError("layernorm: the norm behind a sum works on one residual stream")
+        K.layernorm_post(x, y, alpha, self.params["weight"], self.params["bias"], self.eps, cast)
+
 
 register_norm("rmsnorm", RMSNorm)
 register_norm("layernorm", LayerNorm)

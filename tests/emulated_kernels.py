@@ -115,7 +115,7 @@ def rope_kv_write(qkv, positions, inv_freq, q_out, pool, slots, *, n_heads, n_kv
         pool[page, 1, :, off, :] = x[t, n_heads + n_kv_heads :].to(pool.dtype)
 
 
-def _attend_one(q, pool, table, p, kvh, page_tokens, window, scale, keep_first=0, sink=False):
+def _attend_one(q, pool, table, p, kvh, page_tokens, window, scale, keep_first=0, sink=False, head=0):
     lo = max(0, p - window + 1) if window > 0 else 0
     ts = list(range(0, min(keep_first, lo))) + list(range(lo, p + 1))
     pages = [int(table[t // page_tokens]) for t in ts]
@@ -123,6 +123,9 @@ def _attend_one(q, pool, table, p, kvh, page_tokens, window, scale, keep_first=0
     k = torch.stack([_f(pool[pg, 0, kvh, t % page_tokens]) for pg, t in zip(pages, ts)])
     v = torch.stack([_f(pool[pg, 1, kvh, t % page_tokens]) for pg, t in zip(pages, ts)])
     s = (k @ _f(q)) * scale
+    if isinstance(sink, torch.Tensor):     # a learned score per head, as it is
+        s = torch.cat([s, _f(sink)[head].view(1)])
+        return torch.softmax(s, dim=0)[:-1] @ v
     if sink:
         s = torch.cat([s, s.new_zeros(1)])
         return torch.softmax(s, dim=0)[:-1] @ v
@@ -138,7 +141,7 @@ def _attn(q, pool, out, seg_list, *, seg_q0, seg_qn, seg_ctx, block_table, n_hea
         for i in range(qn):
             for h in range(n_heads):
                 qv = q[q0 + i].view(n_heads, head_dim)[h]
-                o = _attend_one(qv, pool, block_table[seg], ctx + i, h // group, page_tokens, window, scale, keep_first, sink)
+                o = _attend_one(qv, pool, block_table[seg], ctx + i, h // group, page_tokens, window, scale, keep_first, sink, head=h)
                 out[q0 + i].view(n_heads, head_dim)[h] = o.to(out.dtype)
 
 
@@ -359,10 +362,16 @@ def rmsnorm_add(y, w, eps, x):
     x += (ys / torch.sqrt((ys * ys).mean(-1, keepdim=True) + eps) * _f(w)).to(x.dtype)
 
 
-def _turn(x, positions, freq, magnitude, rot_pairs):
-    """x [T, ..., n]: interleaved pairs (2i, 2i + 1), i < rot_pairs, turned by positions[t] * freq[i]."""
+def _turn(x, positions, freq, magnitude, rot_pairs, half_split=False):
+    """x [T, ..., n]: interleaved pairs (2i, 2i + 1), i < rot_pairs, turned by positions[t] * freq[i]; ``half_split``:
+    the pairs (i, i + rot_pairs)."""
     if rot_pairs == 0:
         return x
+    if half_split:
+        n = 2 * rot_pairs
+        mixed = torch.stack([x[..., :rot_pairs], x[..., rot_pairs:n]], -1).reshape(*x.shape[:-1], n)
+        t = _turn(torch.cat([mixed, x[..., n:]], -1), positions, freq, magnitude, rot_pairs)
+        return torch.cat([t[..., 0:n:2], t[..., 1:n:2], t[..., n:]], -1)
     T = x.shape[0]
     ang = positions[:T].to(torch.float64)[:, None] * freq[:rot_pairs].to(torch.float64)[None, :]
     shape = [T] + [1] * (x.dim() - 2) + [rot_pairs]
@@ -376,29 +385,30 @@ def _turn(x, positions, freq, magnitude, rot_pairs):
 
 
 def latent_prep(dqkv, positions, freq, magnitude, w_q, w_kv, eps, cq_out, pool, slots, *, q_rank, kv_rank, rot_dim,
-                rot_pairs, write=True):
+                rot_pairs, write=True, half_split=False):
     T = dqkv.shape[0]
     x = _f(dqkv)
 
     def unit(v):
         return v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps)
 
-    cq_out[:T] = (unit(x[:, :q_rank]) * _f(w_q)).to(cq_out.dtype)
+    if q_rank:
+        cq_out[:T] = (unit(x[:, :q_rank]) * _f(w_q)).to(cq_out.dtype)
     if not write:
         return
     c = unit(x[:, q_rank:q_rank + kv_rank]) * _f(w_kv)
-    kr = _turn(x[:, q_rank + kv_rank:], positions, freq, magnitude, rot_pairs)
+    kr = _turn(x[:, q_rank + kv_rank:q_rank + kv_rank + rot_dim], positions, freq, magnitude, rot_pairs, half_split)
     rows = torch.cat([c, kr], -1).to(pool.dtype)
     page_tokens = pool.shape[-2]
     for t in range(T):
         pool[int(slots[t]) // page_tokens, 0, 0, int(slots[t]) % page_tokens] = rows[t]
 
 
-def latent_q_split(q, positions, freq, magnitude, q_nope_hm, q_rot, *, n_heads, nope_dim, rot_dim, rot_pairs):
+def latent_q_split(q, positions, freq, magnitude, q_nope_hm, q_rot, *, n_heads, nope_dim, rot_dim, rot_pairs, half_split=False):
     T = q.shape[0]
     x = _f(q).view(T, n_heads, nope_dim + rot_dim)
     q_nope_hm[: n_heads * T] = x[..., :nope_dim].transpose(0, 1).reshape(n_heads * T, nope_dim).to(q_nope_hm.dtype)
-    q_rot[:T] = _turn(x[..., nope_dim:], positions, freq, magnitude, rot_pairs).reshape(T, -1).to(q_rot.dtype)
+    q_rot[:T] = _turn(x[..., nope_dim:], positions, freq, magnitude, rot_pairs, half_split).reshape(T, -1).to(q_rot.dtype)
 
 
 def latent_attn(q_abs_hm, q_rot, pool, sink, out_hm, *, seg_q0, seg_qn, seg_ctx, block_table, items, n_items, n_tokens,
@@ -466,6 +476,73 @@ def layernorm(x, w, b, eps, out, rows=None, n_streams=1, coef=None):
     u = (xs * c[None, :, None]).sum(1)
     d = u - u.mean(-1, keepdim=True)
     out.copy_((d / torch.sqrt((d * d).mean(-1, keepdim=True) + eps) * _f(w) + _f(b)).to(out.dtype))
+
+
+def embed_pair(tokens, positions, table, pair, out, *, seg_q0, seg_qn, state_slots, last, n_seg, longest_new, mul_prev, mul_cur):
+    buckets = pair.shape[0] - 1
+    for seg in range(n_seg):
+        q0, qn, slot = int(seg_q0[seg]), int(seg_qn[seg]), int(state_slots[seg])
+        assert qn <= longest_new
+        for i in range(qn):
+            t = q0 + i
+            tok = int(tokens[t])
+            r = buckets
+            if int(positions[t]) > 0:
+                prev = int(tokens[t - 1]) if i > 0 else int(last[slot, 0])
+                r = (prev * mul_prev + tok * mul_cur) % buckets
+            out[t] = (_f(table[tok]) + _f(pair[r])).to(out.dtype)
+    for seg in range(n_seg):
+        if int(seg_qn[seg]) > 0:
+            last[int(state_slots[seg]), 0] = int(tokens[int(seg_q0[seg]) + int(seg_qn[seg]) - 1])
+
+
+def layernorm_post(x, y, alpha, w, b, eps, cast=None):
+    n = x.shape[0]
+    u = alpha * _f(x) + _f(y[:n])
+    d = u - u.mean(-1, keepdim=True)
+    x.copy_((d / torch.sqrt((d * d).mean(-1, keepdim=True) + eps) * _f(w) + _f(b)).to(x.dtype))
+    if cast is not None:
+        cast[:n] = x.to(cast.dtype)
+
+
+def span_rmsnorm(x, spans, eps):
+    for off, n, w in spans:
+        v = _f(x[:, off:off + n])
+        x[:, off:off + n] = (v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps) * _f(w)).to(x.dtype)
+
+
+def glu_clamp(gu, limit, out, *, n_rows=None, row_scale=None, scale_rows=None):
+    n = out.shape[0] if n_rows is None else n_rows
+    inter = out.shape[1]
+    s = 1.0
+    if row_scale is not None:
+        idx = scale_rows[:n].long() if scale_rows is not None else torch.arange(n)
+        s = _f(row_scale)[idx][:, None]
+    g = torch.clamp(_f(gu[:n, :inter]) * s, max=limit)
+    u = torch.clamp(_f(gu[:n, inter:2 * inter]) * s, min=-limit, max=limit)
+    out[:n] = (g / (1.0 + torch.exp(-1.702 * g)) * (u + 1.0)).to(out.dtype)
+
+
+def gla_decay(z, off, n, tau):
+    v = _f(z[:, off:off + n])
+    z[:, off:off + n] = torch.exp(-torch.nn.functional.softplus(-v) / tau).to(z.dtype)
+
+
+def gla_scan(q, off_q, k, off_k, v, off_v, decay, off_a, state, state_offset, state_slots, seg_q0, seg_qn, n_seg, out, *,
+             n_heads, dim, v_dim, q_scale):
+    H, d, dv = n_heads, dim, v_dim
+    for seg in range(n_seg):
+        q0, qn, slot = int(seg_q0[seg]), int(seg_qn[seg]), int(state_slots[seg])
+        S = _f(state[slot, state_offset:state_offset + H * d * dv]).view(H, d, dv).clone()
+        for i in range(qn):
+            r = q0 + i
+            qv = _f(q[r, off_q:off_q + H * d]).view(H, d)
+            kv = _f(k[r, off_k:off_k + H * d]).view(H, d)
+            av = _f(decay[r, off_a:off_a + H * d]).view(H, d)
+            vv = _f(v[r, off_v:off_v + H * dv]).view(H, dv)
+            S = av[:, :, None] * S + kv[:, :, None] * vv[:, None, :]
+            out[r] = (torch.einsum("hdv,hd->hv", S, qv) * q_scale).reshape(-1).to(out.dtype)
+        state[slot, state_offset:state_offset + H * d * dv] = S.reshape(-1).to(state.dtype)
 
 
 def stream_update(x, y, mix, out_coef, n_streams):
@@ -673,7 +750,8 @@ _NAMES = ["embed_rows", "rmsnorm", "rmsnorm_adds", "attn_chunk_tc_takes", "linea
           "moe_sort", "route_small", "route_small_takes", "route_fused_small", "moe_combine", "gather_rows", "apply_penalties", "sample",
           "cast_rows", "rmsnorm_add", "latent_prep", "latent_q_split", "latent_attn", "heads_to_rows", "retention_scan",
           "retention_gate_norm", "head_tile", "latent_attn_mma_takes", "layernorm", "stream_update", "moe_identity",
-          "gated_recurrence", "mlstm_gates", "mlstm_out", "ssm_conv", "ssm_out", "head_prep", "gate_rows", "delta_rule", "delta_out"]
+          "gated_recurrence", "mlstm_gates", "mlstm_out", "ssm_conv", "ssm_out", "head_prep", "gate_rows", "delta_rule", "delta_out",
+          "embed_pair", "layernorm_post", "span_rmsnorm", "glu_clamp", "gla_decay", "gla_scan"]
 
 
 def install(monkeypatch) -> None:
