@@ -5,7 +5,7 @@ sizes (random weights, bfloat16) at batch 8 and context 4096, with the prefill o
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
                     [--config a27b|57b-a14b] [--dtype bf16|fp32] [--trace]
-                    [--design lalepel|pozozen|mekizen [--size m|s] [--kernels]]
+                    [--design lalepel|pozozen|mekizen|gugozen [--size m|s] [--kernels]]
 
 With no options: the headline configuration.  ``--config 57b-a14b``: the Qwen2-57B-A14B layer sizes
 (28 layers, 114.8 GB of weights), decode from 8,192-token contexts and a 32,768-token prefill in portions
@@ -13,7 +13,7 @@ of 2,048.  ``--dtype fp32``: the true 32-bit path (CUDA-core products, float32 c
 a mixed continuous-batching trace through ``Engine`` (32 requests, prompts uniform in [16, 4096], decode
 lengths uniform in [1, 512], one arrival every 4 steps, portions of 512 tokens).
 
-``--design lalepel`` / ``pozozen`` / ``mekizen``: another workload altogether, that design's prefill and decode throughput at
+``--design lalepel`` / ``pozozen`` / ``mekizen`` / ``gugozen``: another workload altogether, that design's prefill and decode throughput at
 real layer sizes beside this architecture's (and, for Mekizen, Pozozen's) at equal sizes (``locus_b200/tools/arch_bench.py``).
 
 Prints one JSON line.  ``value``: decoded tokens per second of K decode steps timed on the
@@ -146,7 +146,7 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--step-tokens", type=int, default=0, help="most tokens of a step (default: the configuration's)")
-    ap.add_argument("--design", default="", choices=["", "lalepel", "pozozen", "mekizen"],
+    ap.add_argument("--design", default="", choices=["", "lalepel", "pozozen", "mekizen", "gugozen"],
                     help="instead of the headline workload: prefill and decode throughput of this design at real layer "
                          "sizes beside Qwen2-MoE at equal sizes (locus_b200.tools.arch_bench; --size, --kernels)")
     ap.add_argument("--size", default="m", choices=["m", "s"], help="layer sizes of --design")

@@ -780,42 +780,3 @@ extern "C" int locus_span_rmsnorm(float* x, int ld, int T, int off0, int n0, con
                  w_dt, eps);
     return locus_launch_status();
 }
-
-// ---------------------------------------------------------------------------
-// The activation of a clamped gated unit over float32 rows [g | u] (row stride ld; g the first I columns, u the next I:
-// the two products of the same input, made as one):
-//     g' = min(s g, limit),  u' = clamp(s u, -limit, limit),  out = g' sigmoid(1.702 g') (u' + 1),
-// with s = row_scale[scale_rows ? scale_rows[m] : m] (a weight on the unit's INPUT, which both products carry as a
-// factor; null: 1).
-template <typename TO>
-__global__ void __launch_bounds__(256) glu_clamp_kernel(const float* __restrict__ gu, long long ld,
-                                                        const float* __restrict__ row_scale,
-                                                        const int* __restrict__ scale_rows, float limit,
-                                                        TO* __restrict__ out, int I, long long total) {
-    pdl_entry();
-    pdl_trigger();
-    const long long i = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
-    if (i >= total) return;
-    const long long m = i / I;
-    const float s = row_scale ? row_scale[scale_rows ? scale_rows[m] : m] : 1.0f;
-    const float* row = gu + m * ld + (i - m * I);
-    const float gv = fminf(row[0] * s, limit), uv = fminf(fmaxf(row[I] * s, -limit), limit);
-    out[i] = from_f<TO>(gv / (1.0f + expf(-1.702f * gv)) * (uv + 1.0f));
-}
-
-extern "C" int locus_glu_clamp(const float* gu, long long ld, const float* row_scale, const int* scale_rows, float limit,
-                               void* out, int out_dt, int n, int I, cudaStream_t stream) {
-    if (n <= 0) return 0;
-    if (I <= 0 || ld < 2LL * I) return LOCUS_ERR_UNSUPPORTED;
-    const long long total = static_cast<long long>(n) * I, blocks = (total + 255) / 256;
-    if (blocks > 0x7fffffffLL) return LOCUS_ERR_UNSUPPORTED;
-    if (out_dt == LOCUS_DT_BF16)
-        locus_launch(glu_clamp_kernel<bf16>, dim3(static_cast<unsigned>(blocks)), dim3(256), 0, stream, gu, ld, row_scale,
-                     scale_rows, limit, static_cast<bf16*>(out), I, total);
-    else if (out_dt == LOCUS_DT_F32)
-        locus_launch(glu_clamp_kernel<float>, dim3(static_cast<unsigned>(blocks)), dim3(256), 0, stream, gu, ld, row_scale,
-                     scale_rows, limit, static_cast<float*>(out), I, total);
-    else
-        return LOCUS_ERR_UNSUPPORTED;
-    return locus_launch_status();
-}

@@ -28,7 +28,10 @@ struct GemmArgs {
     void* out;
     int out_dt;
     int accumulate;          // out (float32) += result
-    int act;                 // 0: none; 1: relu(v)^2 (after the bias, before the row scale)
+    int act;                 // 0: none; 1: relu(v)^2 (after the bias, before the row scale); 2 (with w2): the clamped
+                             // gated unit g' sigmoid(1.702 g') (u' + 1), g' = min(s g, limit), u' = clamp(s u, +-limit),
+                             // s the row's scale, which then stands for a factor on the input
+    float act_param;         // the limit of act 2
     const float* row_scale;  // or null: row m is scaled by row_scale[scale_rows ? scale_rows[m] : m]
     const int* scale_rows;
     const int* x_rows;       // [M] or null
@@ -136,7 +139,11 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(GemmArgs a) {
             const int n = col0 + tx * 4 + j;
             if (n >= a.N) continue;
             float v = acc[i][j];
-            if (SWIGLU) {
+            if (SWIGLU && a.act == 2) {
+                const float g = fminf(v * rs, a.act_param);
+                const float u = fminf(fmaxf(acc2[i][j] * rs, -a.act_param), a.act_param);
+                v = g / (1.0f + expf(-1.702f * g)) * (u + 1.0f);
+            } else if (SWIGLU) {
                 const float g = v;
                 v = g / (1.0f + expf(-g)) * acc2[i][j];
             }
@@ -145,7 +152,7 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(GemmArgs a) {
                 v = fmaxf(v, 0.f);
                 v *= v;
             }
-            if (a.row_scale) v *= rs;
+            if (a.row_scale && a.act != 2) v *= rs;
             const size_t o = static_cast<size_t>(r) * a.ldo + n;
             if (a.accumulate) {
                 static_cast<float*>(a.out)[o] += v;
@@ -170,24 +177,24 @@ static int launch(const GemmArgs& a, int max_tiles, bool swiglu, cudaStream_t st
 }
 
 // x_dt / w_dt: element types of x and of W (and W2).  flags: bit 0 = add the result into the float32 out,
-// bit 1 = the squared-ReLU activation (not with W2).  max_tiles: number of 64-row tiles
+// bits 1-2 = the activation: 1 squared ReLU (not with W2), 2 the clamped gated unit with limit act_param (with W2).  max_tiles: number of 64-row tiles
 // to launch; for a grouped product an upper bound (tiles past *n_tiles return at once).
 extern "C" int locus_gemm_simt(const void* x, int x_dt, const void* w, const void* w2, int w_dt,
                                const void* bias, int bias_dt, void* out, int out_dt,
-                               int flags, const float* row_scale, const int* scale_rows,
+                               int flags, float act_param, const float* row_scale, const int* scale_rows,
                                const int* x_rows,
                                int x_row_div, int M, int N, int K, long long ldx, long long ldo,
                                const int* tile_expert, const int* tile_row0,
                                const int* tile_rows, const int* n_tiles, int max_tiles,
                                long long w_expert_stride, cudaStream_t stream) {
     if (N <= 0 || K <= 0) return LOCUS_ERR_UNSUPPORTED;
-    const int accumulate = flags & 1, act = (flags >> 1) & 1;
-    if (act && w2 != nullptr) return LOCUS_ERR_UNSUPPORTED;
+    const int accumulate = flags & 1, act = (flags >> 1) & 3;
+    if ((act == 1 && w2 != nullptr) || (act == 2 && w2 == nullptr) || act == 3) return LOCUS_ERR_UNSUPPORTED;
     if (accumulate && out_dt != LOCUS_DT_F32) return LOCUS_ERR_UNSUPPORTED;
     if (x_rows != nullptr && x_row_div <= 0) return LOCUS_ERR_UNSUPPORTED;
     GemmArgs a;
     a.x = x; a.w = w; a.w2 = w2; a.bias = bias; a.bias_dt = bias_dt; a.out = out;
-    a.out_dt = out_dt; a.accumulate = accumulate; a.act = act; a.row_scale = row_scale; a.scale_rows = scale_rows; a.x_rows = x_rows;
+    a.out_dt = out_dt; a.accumulate = accumulate; a.act = act; a.act_param = act_param; a.row_scale = row_scale; a.scale_rows = scale_rows; a.x_rows = x_rows;
     a.x_row_div = x_row_div; a.M = M; a.N = N; a.K = K; a.ldx = ldx; a.ldo = ldo;
     a.tile_expert = tile_expert; a.tile_row0 = tile_row0; a.tile_rows = tile_rows;
     a.n_tiles = n_tiles; a.w_expert_stride = w_expert_stride;

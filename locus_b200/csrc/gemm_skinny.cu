@@ -28,7 +28,8 @@ struct SkinnyArgs {
     void* out;
     int out_dt;
     int accumulate;
-    int act;  // 1: relu(v)^2 after the bias, before the row scale
+    int act;  // 1: relu(v)^2 after the bias, before the row scale; 2 (two weights): the clamped gated unit of gemm_simt.cu
+    float act_param;
     const float* row_scale;
     const int* scale_rows;
     const int* x_rows;
@@ -195,14 +196,20 @@ __global__ void __launch_bounds__(32 * SK_WARPS, ROUTE ? 1 : (NT == 1 ? 4 : ((NT
             v += red[static_cast<size_t>(w) * SETS * NT * 128 + idx];
             if (DUAL) u += red[static_cast<size_t>(w) * SETS * NT * 128 + NT * 128 + idx];
         }
-        if (DUAL) v = v / (1.0f + expf(-v)) * u;
+        const int row = tok0 + t;
+        const float rs = a.row_scale ? a.row_scale[a.scale_rows ? a.scale_rows[row] : row] : 1.0f;
+        if (DUAL && a.act == 2) {
+            const float g = fminf(v * rs, a.act_param), uc = fminf(fmaxf(u * rs, -a.act_param), a.act_param);
+            v = g / (1.0f + expf(-1.702f * g)) * (uc + 1.0f);
+        } else if (DUAL) {
+            v = v / (1.0f + expf(-v)) * u;
+        }
         if (a.bias) v += ld_dyn(a.bias, a.bias_dt, n);
         if (a.act == 1) {
             v = fmaxf(v, 0.f);
             v *= v;
         }
-        const int row = tok0 + t;
-        if (a.row_scale) v *= a.row_scale[a.scale_rows ? a.scale_rows[row] : row];
+        if (a.row_scale && a.act != 2) v *= rs;
         const size_t o = static_cast<size_t>(row) * a.ldo + n;
         if (a.accumulate) {
             static_cast<float*>(a.out)[o] += v;
@@ -256,14 +263,14 @@ static int launch(const SkinnyArgs& a, int tiles, bool dual, cudaStream_t stream
 // tile_tokens: 8, 16 or 32 rows of x per tile (for a grouped product: the tile size of the
 // tile list).  x and W bfloat16; K a multiple of 8; 16-byte aligned rows.
 extern "C" int locus_gemm_skinny(const void* x, const void* w, const void* w2, const void* bias, int bias_dt,
-                                 void* out, int out_dt, int flags, const float* row_scale,
+                                 void* out, int out_dt, int flags, float act_param, const float* row_scale,
                                  const int* scale_rows, const int* x_rows, int x_row_div, int M, int N, int K,
                                  long long ldx, long long ldo, int tile_tokens, const int* tile_expert,
                                  const int* tile_row0, const int* tile_rows, const int* n_tiles, int max_tiles,
                                  long long w_expert_stride, int lists_ready, cudaStream_t stream) {
     if (N <= 0 || K <= 0 || K % 8 != 0 || ldx % 8 != 0) return LOCUS_ERR_UNSUPPORTED;
-    const int accumulate = flags & 1, act = (flags >> 1) & 1;  // bit 0: add into out; bit 1: squared ReLU
-    if (act && w2 != nullptr) return LOCUS_ERR_UNSUPPORTED;
+    const int accumulate = flags & 1, act = (flags >> 1) & 3;  // bit 0: add into out; bits 1-2: the activation
+    if ((act == 1 && w2 != nullptr) || (act == 2 && w2 == nullptr) || act == 3) return LOCUS_ERR_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(w2)) & 15)
         return LOCUS_ERR_UNSUPPORTED;
     if (accumulate && out_dt != LOCUS_DT_F32) return LOCUS_ERR_UNSUPPORTED;
@@ -272,7 +279,7 @@ extern "C" int locus_gemm_skinny(const void* x, const void* w, const void* w2, c
     SkinnyArgs a;
     a.x = static_cast<const bf16*>(x); a.w = static_cast<const bf16*>(w); a.w2 = static_cast<const bf16*>(w2);
     a.bias = bias; a.bias_dt = bias_dt; a.out = out; a.out_dt = out_dt; a.accumulate = accumulate; a.act = act;
-    a.row_scale = row_scale; a.scale_rows = scale_rows; a.x_rows = x_rows; a.x_row_div = x_row_div;
+    a.act_param = act_param; a.row_scale = row_scale; a.scale_rows = scale_rows; a.x_rows = x_rows; a.x_row_div = x_row_div;
     a.M = M; a.N = N; a.K = K; a.ldx = ldx; a.ldo = ldo; a.tile_expert = tile_expert; a.tile_row0 = tile_row0;
     a.tile_rows = tile_rows; a.n_tiles = n_tiles; a.w_expert_stride = w_expert_stride;
     a.lists_ready = lists_ready;

@@ -62,7 +62,10 @@ struct TileGeom {
 struct TcArgs {
     int M, N, K, TN, dual, stages, tmem_cols, tiles_x, tiles_y, acc_bufs;
     int accumulate;
-    int act;  // 1: relu(v)^2 after the bias, before the row scale (never with a product split along K)
+    int act;  // 1: relu(v)^2 after the bias, before the row scale (never with a product split along K); 2 (two weights):
+              // the clamped gated unit g' sigmoid(1.702 g') (u' + 1), g' = min(s g, limit), u' = clamp(s u, +-limit), s the
+              // row's scale (then a factor on the input)
+    float act_param;  // the limit of act 2
     void* out;
     int out_dt;
     long long ldo;
@@ -428,6 +431,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 }
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 float val[16];
+                if (DUAL && a.act == 2) {
+                    const float lim = a.act_param;
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const float s = a.row_scale ? scales[c0 + j] : 1.0f;
+                        const float g = fminf(__uint_as_float(v[j]) * s, lim);
+                        const float uc = fminf(fmaxf(__uint_as_float(u[j]) * s, -lim), lim);
+                        val[j] = __fdividef(g, 1.0f + __expf(-1.702f * g)) * (uc + 1.0f) + bias;
+                    }
+                } else
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
                     float x = __uint_as_float(v[j]);
@@ -601,13 +614,13 @@ static int pow2_at_least(int v) {
 // kernel adds them in order and does the epilogue.  The splits are renumbered so that none is empty.
 extern "C" int locus_gemm_tc(const void* x, long long x_rows_total, long long ldx, const void* w, const void* w2,
                              long long w_rows_total, const void* bias, int bias_dt, void* out, int out_dt,
-                             int flags, const float* row_scale, const int* scale_rows, int M, int N, int K,
+                             int flags, float act_param, const float* row_scale, const int* scale_rows, int M, int N, int K,
                              long long ldo, int TN, const int* tile_expert, const int* tile_row0,
                              const int* tile_rows, const int* n_tiles, int max_tiles, float* split_scratch,
                              int splits, cudaStream_t stream) {
     const int dual = w2 != nullptr ? 1 : 0;
-    const int accumulate = flags & 1, act = (flags >> 1) & 1;  // bit 0: add into out; bit 1: squared ReLU
-    if (act && (dual || splits > 1)) return LOCUS_ERR_UNSUPPORTED;
+    const int accumulate = flags & 1, act = (flags >> 1) & 3;  // bit 0: add into out; bits 1-2: the activation
+    if ((act == 1 && (dual || splits > 1)) || (act == 2 && (!dual || splits > 1)) || act == 3) return LOCUS_ERR_UNSUPPORTED;
     if (N <= 0 || K <= 0 || K % 8 != 0 || ldx % 8 != 0) return LOCUS_ERR_UNSUPPORTED;
     if (TN < 16 || TN > 256 || TN % 16 != 0 || (dual && TN > 256)) return LOCUS_ERR_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(w2)) & 15)
@@ -662,6 +675,7 @@ extern "C" int locus_gemm_tc(const void* x, long long x_rows_total, long long ld
     const bool split = a.splits > 1;
     a.accumulate = split ? 0 : accumulate;
     a.act = act;
+    a.act_param = act_param;
     a.out = split ? split_scratch : out;
     a.out_dt = split ? LOCUS_DT_F32 : out_dt;
     a.ldo = split ? N : ldo;

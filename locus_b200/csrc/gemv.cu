@@ -22,7 +22,8 @@ struct GemvArgs {
     void* out;
     int out_dt;
     int accumulate;
-    int act;  // 1: relu(v)^2 after the bias, before the row scale
+    int act;  // 1: relu(v)^2 after the bias, before the row scale; 2 (two weights): the clamped gated unit of gemm_simt.cu
+    float act_param;
     const float* row_scale;
     const int* scale_rows;
     const int* x_rows;
@@ -166,14 +167,20 @@ __global__ void __launch_bounds__(32 * GV_WARPS) rowstream_kernel(GemvArgs a) {
         float v = warp_sum(acc[t]);
         float u = DUAL ? warp_sum(acc2[t]) : 0.f;
         if (lane != 0) continue;
-        if (DUAL) v = v / (1.0f + expf(-v)) * u;
+        const int r = row0 + t;
+        const float rs = a.row_scale ? a.row_scale[a.scale_rows ? a.scale_rows[r] : r] : 1.0f;
+        if (DUAL && a.act == 2) {
+            const float g = fminf(v * rs, a.act_param), uc = fminf(fmaxf(u * rs, -a.act_param), a.act_param);
+            v = g / (1.0f + expf(-1.702f * g)) * (uc + 1.0f);
+        } else if (DUAL) {
+            v = v / (1.0f + expf(-v)) * u;
+        }
         if (a.bias) v += ld_dyn(a.bias, a.bias_dt, n);
         if (a.act == 1) {
             v = fmaxf(v, 0.f);
             v *= v;
         }
-        const int r = row0 + t;
-        if (a.row_scale) v *= a.row_scale[a.scale_rows ? a.scale_rows[r] : r];
+        if (a.row_scale && a.act != 2) v *= rs;
         const size_t o = static_cast<size_t>(r) * a.ldo + n;
         if (a.accumulate) {
             static_cast<float*>(a.out)[o] += v;
@@ -200,21 +207,21 @@ static int launch(const GemvArgs& a, int tiles, bool dual, cudaStream_t stream) 
 // 16-byte (bfloat16) / 32-byte (float32) boundaries, and, for a grouped product, tiles of at
 // most 8 rows.
 extern "C" int locus_gemv(const void* x, int x_dt, const void* w, const void* w2, int w_dt, const void* bias,
-                          int bias_dt, void* out, int out_dt, int flags, const float* row_scale,
+                          int bias_dt, void* out, int out_dt, int flags, float act_param, const float* row_scale,
                           const int* scale_rows, const int* x_rows, int x_row_div, int M, int N, int K,
                           long long ldx, long long ldo, const int* tile_expert, const int* tile_row0,
                           const int* tile_rows, const int* n_tiles, int max_tiles, long long w_expert_stride,
                           cudaStream_t stream) {
     if (N <= 0 || K <= 0 || K % 8 != 0 || ldx % 8 != 0) return LOCUS_ERR_UNSUPPORTED;
-    const int accumulate = flags & 1, act = (flags >> 1) & 1;  // the flags of locus_gemm_simt
-    if (act && w2 != nullptr) return LOCUS_ERR_UNSUPPORTED;
+    const int accumulate = flags & 1, act = (flags >> 1) & 3;  // the flags of locus_gemm_simt
+    if ((act == 1 && w2 != nullptr) || (act == 2 && w2 == nullptr) || act == 3) return LOCUS_ERR_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(w2)) & 31)
         return LOCUS_ERR_UNSUPPORTED;
     if (accumulate && out_dt != LOCUS_DT_F32) return LOCUS_ERR_UNSUPPORTED;
     if (x_rows != nullptr && x_row_div <= 0) return LOCUS_ERR_UNSUPPORTED;
     GemvArgs a;
     a.x = x; a.w = w; a.w2 = w2; a.bias = bias; a.bias_dt = bias_dt; a.out = out; a.out_dt = out_dt;
-    a.accumulate = accumulate; a.act = act; a.row_scale = row_scale; a.scale_rows = scale_rows; a.x_rows = x_rows;
+    a.accumulate = accumulate; a.act = act; a.act_param = act_param; a.row_scale = row_scale; a.scale_rows = scale_rows; a.x_rows = x_rows;
     a.x_row_div = x_row_div; a.M = M; a.N = N; a.K = K; a.ldx = ldx; a.ldo = ldo;
     a.tile_expert = tile_expert; a.tile_row0 = tile_row0; a.tile_rows = tile_rows; a.n_tiles = n_tiles;
     a.w_expert_stride = w_expert_stride;

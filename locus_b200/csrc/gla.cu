@@ -3,11 +3,14 @@
 //
 //     S_t = diag(a_t) S_(t-1) + k_t v_t^T,      o_t = S_t^T q_t * q_scale,
 //
-// with a_t [d] in (0, 1) per token and head.  Everything is float32; q, k, v and a are columns of float32 row matrices
-// given by pointer, row stride and offset.
+// with a_t [d] in (0, 1) per token and head.  Everything is float32; q, k, v and the decays are columns of float32 row
+// matrices given by pointer, row stride and offset.  The decays travel as c = 1 - a and a row is decayed as S - c S: a
+// channel that forgets slowly has a within a few float32 spacings of 1, so that a itself would carry its rate 1 - a
+// with a relative error of 1e-4 and more, which a few hundred tokens turn into as much in the state; c keeps the rate
+// to float32's own precision.
 //
-//   gla_decay   a = sigmoid(z)^(1 / tau) = exp(-softplus(-z) / tau) in place over rows of logits z (softplus in its stable
-//               form max(x, 0) + log1p(exp(-|x|)); no fast-math)
+//   gla_decay   c = 1 - sigmoid(z)^(1 / tau) = -expm1(-softplus(-z) / tau) in place over rows of logits z (softplus in its
+//               stable form max(x, 0) + log1p(exp(-|x|)); no fast-math)
 //   gla_scan    a warp owns GL_CW = 4 columns of one head's state for one request and walks the request's new tokens in
 //               order.  Its lanes are 8 groups of rows x 4 columns: lane (lr, lc) keeps, of column lc, the rows
 //               32 j + 4 lr + {0, 1, 2, 3} (j = 0, 1, ...; d <= 256) in registers, so a token's read-out crosses 8
@@ -21,7 +24,7 @@ struct GlaArgs {
     const float* q;
     const float* k;
     const float* v;
-    const float* a;
+    const float* a;       // 1 - decay
     float* state;
     const int* state_slots;
     const int* seg_q0;
@@ -105,8 +108,8 @@ __global__ void __launch_bounds__(128) gla_scan_kernel(const GlaArgs a, int col_
         float o0 = 0.f, o1 = 0.f;
 #pragma unroll
         for (int i = 0; i < R; i += 2) {
-            s[i] = fmaf(aa[i], s[i], kk[i] * vv);
-            s[i + 1] = fmaf(aa[i + 1], s[i + 1], kk[i + 1] * vv);
+            s[i] = fmaf(kk[i], vv, fmaf(-aa[i], s[i], s[i]));
+            s[i + 1] = fmaf(kk[i + 1], vv, fmaf(-aa[i + 1], s[i + 1], s[i + 1]));
             o0 = fmaf(s[i], qq[i], o0);
             o1 = fmaf(s[i + 1], qq[i + 1], o1);
         }
@@ -149,7 +152,7 @@ extern "C" int locus_gla_scan(const float* q, int ldq, int off_q, const float* k
     return locus_launch_status();
 }
 
-// z [T, ld] float32, columns [off, off + n): z <- exp(-softplus(-z) / tau).
+// z [T, ld] float32, columns [off, off + n): z <- 1 - exp(-softplus(-z) / tau).
 __global__ void __launch_bounds__(256) gla_decay_kernel(float* __restrict__ z, int ld, int off, int n, float inv_tau,
                                                         long long total) {
     pdl_entry();
@@ -159,7 +162,7 @@ __global__ void __launch_bounds__(256) gla_decay_kernel(float* __restrict__ z, i
     float* p = z + (i / n) * ld + off + (i % n);
     const float x = -*p;                                          // softplus(x) = max(x, 0) + log1p(exp(-|x|))
     const float sp = fmaxf(x, 0.f) + log1pf(expf(-fabsf(x)));
-    *p = expf(-sp * inv_tau);
+    *p = -expm1f(-sp * inv_tau);
 }
 
 extern "C" int locus_gla_decay(float* z, int ld, int off, int n, int T, float tau, cudaStream_t stream) {

@@ -57,8 +57,11 @@ __device__ __forceinline__ void select_token(const float* __restrict__ lg, float
         for (int x = lane; x < E; x += 32) p[x] = 1.0f / (1.0f + expf(-__ldcg(lg + x)));
     }
     if (has_gate && lane == 0) gamma[t] = 1.0f / (1.0f + expf(-__ldcg(lg + E)));
+    // Sigmoid scores with nothing added and no groups are ranked by their logits: the same order, and logits that a
+    // sigmoid far from zero rounds to one score stay apart.
+    const bool by_logit = (o.score_fn & SCORE_FN_MASK) == SCORE_SIGMOID && o.sel_bias == nullptr && o.n_group <= 1;
     for (int x = lane; x < E; x += 32) {
-        const float v = p[x] + (o.sel_bias != nullptr ? o.sel_bias[x] : 0.f);
+        const float v = by_logit ? __ldcg(lg + x) : p[x] + (o.sel_bias != nullptr ? o.sel_bias[x] : 0.f);
         sel[x] = (v == v) ? v : -3.0e38f;
     }
     __syncwarp();

@@ -432,7 +432,7 @@ def expert_tile(n_pairs: int, n_experts: int) -> int:
 
 
 # activations of a product's epilogue, by their code in the kernels' flags
-ACTIVATIONS = {None: 0, "relu2": 1}
+ACTIVATIONS = {None: 0, "relu2": 1, "glu_clamp": 2}
 
 
 def tc_error() -> int:
@@ -446,10 +446,13 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, w2: Optional[
            row_scale: Optional[torch.Tensor] = None, scale_rows: Optional[torch.Tensor] = None,
            x_rows: Optional[torch.Tensor] = None, x_row_div: int = 1, layout: Optional[ExpertLayout] = None,
            n_rows: Optional[int] = None, lists_ready: bool = False, second_tiles: bool = False,
-           act: Optional[str] = None) -> None:
+           act: Optional[str] = None, act_limit: float = 0.0) -> None:
     """out = x . w^T with float32 accumulation on CUDA cores (see csrc/gemm_simt.cu).
 
-    ``w2``: out = silu(x . w^T) * (x . w2^T).  ``act`` = "relu2": out = max(x . w^T + bias, 0)^2 (not with ``w2``).  ``bias`` [N] is added, ``row_scale`` [M]
+    ``w2``: out = silu(x . w^T) * (x . w2^T).  ``act`` = "relu2": out = max(x . w^T + bias, 0)^2 (not with ``w2``).
+    ``act`` = "glu_clamp" (with ``w2``): the clamped gated unit out = g sigmoid(1.702 g) (u + 1) with g = min(s x . w^T,
+    ``act_limit``), u = clamp(s x . w2^T, -act_limit, act_limit), where s is the row's ``row_scale`` (1 without): the
+    scale then stands for a factor on the row of x and is not applied once more behind the activation.  ``bias`` [N] is added, ``row_scale`` [M]
     multiplies the row (``scale_rows``: row m uses row_scale[scale_rows[m]]), ``accumulate`` adds the result into the float32 ``out``.
     ``x_rows``: logical row m reads x[x_rows[m] // x_row_div].  ``layout``: grouped product,
     ``w`` is [E, N, K] and logical rows are the expert-sorted pairs of the layout.
@@ -475,7 +478,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, w2: Optional[
         _need(w2.shape == w.shape and w2.dtype == w.dtype and w2.is_contiguous(), "linear: w2 must match w")
     if accumulate:
         _need(out.dtype == torch.float32, "linear: accumulate needs a float32 out")
-    _need(act in ACTIVATIONS and not (act and w2 is not None), f"linear: activation {act!r} (known: relu2; not with w2)")
+    _need(act in ACTIVATIONS and not (act == "relu2" and w2 is not None) and not (act == "glu_clamp" and (w2 is None or not act_limit > 0)),
+          f"linear: activation {act!r} (known: relu2 without w2; glu_clamp with w2 and a positive act_limit)")
     flags = I((1 if accumulate else 0) | (ACTIVATIONS[act] << 1))
     if bias is not None:
         _need(bias.numel() == N and bias.is_contiguous(), "linear: bias size")
@@ -504,7 +508,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, w2: Optional[
             max_tiles = stride = 0
         code = _lib("gemm_skinny").locus_gemm_skinny(
             _p(x), _p(w), _p(w2), _p(bias), I(dtype_code(bias.dtype) if bias is not None else 0), _p(out),
-            I(dtype_code(out.dtype)), flags, _p(row_scale), _p(scale_rows), _p(x_rows),
+            I(dtype_code(out.dtype)), flags, F(act_limit), _p(row_scale), _p(scale_rows), _p(x_rows),
             I(x_row_div), I(M), I(N), I(K), LL(x.stride(0)), LL(out.stride(0)), I(tile), _p(te), _p(t0), _p(tr),
             _p(nt), I(max_tiles), LL(stride), I(1 if (lists_ready and layout is not None) else 0), _stream()
         )
@@ -522,7 +526,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, w2: Optional[
         code = _lib("gemv").locus_gemv(
             _p(x), I(dtype_code(x.dtype)), _p(w), _p(w2), I(dtype_code(w.dtype)), _p(bias),
             I(dtype_code(bias.dtype) if bias is not None else 0), _p(out), I(dtype_code(out.dtype)),
-            flags, _p(row_scale), _p(scale_rows), _p(x_rows), I(x_row_div), I(M), I(N), I(K),
+            flags, F(act_limit), _p(row_scale), _p(scale_rows), _p(x_rows), I(x_row_div), I(M), I(N), I(K),
             LL(x.stride(0)), LL(out.stride(0)), _p(te), _p(t0), _p(tr), _p(nt), I(max_tiles), LL(stride), _stream()
         )
         _check(code, "linear", f"(few rows; M={M}, N={N}, K={K}, x {x.dtype}, w {w.dtype})")
@@ -550,7 +554,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, w2: Optional[
         code = _lib("gemm_tc").locus_gemm_tc(
             _p(x), LL(M), LL(x.stride(0)), _p(w), _p(w2), LL(w.numel() // K), _p(bias),
             I(dtype_code(bias.dtype) if bias is not None else 0), _p(out), I(dtype_code(out.dtype)),
-            flags, _p(row_scale), _p(scale_rows), I(M), I(N), I(K), LL(out.stride(0)), I(TN),
+            flags, F(act_limit), _p(row_scale), _p(scale_rows), I(M), I(N), I(K), LL(out.stride(0)), I(TN),
             _p(te), _p(t0), _p(tr), _p(nt), I(max_tiles), _p(scratch if splits > 1 else None), I(splits), _stream()
         )
         if splits > 1 and code == 0:
@@ -570,7 +574,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, w2: Optional[
     code = _lib("gemm_simt").locus_gemm_simt(
         _p(x), I(dtype_code(x.dtype)), _p(w), _p(w2), I(dtype_code(w.dtype)), _p(bias),
         I(dtype_code(bias.dtype) if bias is not None else 0), _p(out), I(dtype_code(out.dtype)),
-        flags, _p(row_scale), _p(scale_rows), _p(x_rows), I(x_row_div), I(M), I(N), I(K),
+        flags, F(act_limit), _p(row_scale), _p(scale_rows), _p(x_rows), I(x_row_div), I(M), I(N), I(K),
         LL(x.stride(0)), LL(out.stride(0)), _p(te), _p(t0), _p(tr), _p(nt), I(max_tiles), LL(stride),
         _stream()
     )
@@ -1801,8 +1805,8 @@ def delta_out(o: torch.Tensor, proj: torch.Tensor, off_g: int, w: torch.Tensor, 
 
 
 # ---------------------------------------------------------------------------
-# an embedding with a hashed pair table, the norm of a post-norm layer, a norm over spans of columns, a clamped gated
-# unit (csrc/elementwise.cu); gated linear attention (csrc/gla.cu)
+# an embedding with a hashed pair table, the norm of a post-norm layer, a norm over spans of columns
+# (csrc/elementwise.cu); gated linear attention (csrc/gla.cu)
 
 
 def embed_pair(tokens: torch.Tensor, positions: torch.Tensor, table: torch.Tensor, pair: torch.Tensor, out: torch.Tensor, *,
@@ -1865,31 +1869,12 @@ def span_rmsnorm(x: torch.Tensor, spans, eps: float) -> None:
     _check(code, "span_rmsnorm")
 
 
-def glu_clamp(gu: torch.Tensor, limit: float, out: torch.Tensor, *, n_rows: Optional[int] = None,
-              row_scale: Optional[torch.Tensor] = None, scale_rows: Optional[torch.Tensor] = None) -> None:
-    """out = g' sigmoid(1.702 g') (u' + 1) with g' = min(s g, limit), u' = clamp(s u, -limit, limit) over float32 rows
-    ``gu`` [n, 2 I] = [g | u]; s = row_scale[scale_rows[m] if scale_rows else m] (a weight on the unit's input, which
-    both products carry as a factor; None: 1)."""
-    _f32c(gu, "glu_clamp: gu")
-    _cuda_c(out, "out")
-    n = out.shape[0] if n_rows is None else n_rows
-    inter = out.shape[1]
-    _need(gu.dim() == 2 and gu.shape[1] == 2 * inter and gu.shape[0] >= n and out.shape[0] >= n, "glu_clamp: shapes")
-    if row_scale is not None:
-        _need(row_scale.dtype == torch.float32 and row_scale.is_contiguous(), "glu_clamp: row_scale must be float32")
-        if scale_rows is not None:
-            _i32(scale_rows, "scale_rows")
-    code = _lib("elementwise").locus_glu_clamp(_p(gu), LL(gu.stride(0)), _p(row_scale),
-                                               _p(scale_rows if row_scale is not None else None), F(limit), _p(out),
-                                               I(dtype_code(out.dtype)), I(n), I(inter), _stream())
-    _check(code, "glu_clamp")
-
-
 GLA_MAX_DIM = 256
 
 
 def gla_decay(z: torch.Tensor, off: int, n: int, tau: float) -> None:
-    """z[:, off : off + n] <- sigmoid(z)^(1 / tau) in place on float32 rows, as exp(-softplus(-z) / tau)."""
+    """z[:, off : off + n] <- 1 - sigmoid(z)^(1 / tau) in place on float32 rows, as -expm1(-softplus(-z) / tau): what a
+    row of the state loses per token (the form :func:`gla_scan` takes: near 1 a decay itself is too coarse in float32)."""
     _f32c(z, "gla_decay: z")
     _need(z.stride(1) == 1 and 0 <= off and off + n <= z.shape[1], "gla_decay: columns")
     code = _lib("gla").locus_gla_decay(_p(z), I(z.stride(0)), I(off), I(n), I(z.shape[0]), F(tau), _stream())
@@ -1900,8 +1885,8 @@ def gla_scan(q: torch.Tensor, off_q: int, k: torch.Tensor, off_k: int, v: torch.
              off_a: int, state: torch.Tensor, state_offset: int, state_slots: torch.Tensor, seg_q0: torch.Tensor,
              seg_qn: torch.Tensor, n_seg: int, out: torch.Tensor, *, n_heads: int, dim: int, v_dim: int, q_scale: float) -> None:
     """Gated linear attention per request and head over every segment's new tokens in order, from and into the request's
-    state slot: S <- diag(a_t) S + k_t v_t^T; o_t = S^T q_t * q_scale.  ``q``, ``k``, ``decay`` (a_t, one factor per key
-    channel) and ``v``: float32 row matrices in which head h's columns start at ``off_*`` + h * dim (``off_v`` + h * v_dim);
+    state slot: S <- diag(a_t) S + k_t v_t^T; o_t = S^T q_t * q_scale.  ``q``, ``k``, ``decay`` (1 - a_t, one number per
+    key channel: :func:`gla_decay`) and ``v``: float32 row matrices in which head h's columns start at ``off_*`` + h * dim (``off_v`` + h * v_dim);
     head h's state [dim, v_dim] starts ``state_offset`` + h * dim * v_dim floats into a slot of ``state`` [n_slots,
     floats]; ``out`` [T, n_heads * v_dim] float32."""
     for t, name in ((q, "q"), (k, "k"), (v, "v"), (decay, "decay"), (out, "out")):

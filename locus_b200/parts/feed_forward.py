@@ -15,9 +15,9 @@ Further forms: ``activation`` "relu2" (down(max(up h, 0)^2), no gate matrix) and
 
     g = min(W_gate h, limit),  u = clamp(W_up h, -limit, limit),  out = W_down (g sigmoid(1.702 g) (u + 1)),
 
-whose two first products are one product against the stacked weight [gate | up] with a float32 result; and
-``weight_on_input``: a picked expert's weight multiplies its input, out = sum expert_e(w_e h), not its output (the two
-first products carry the weight as a factor, so it enters in front of the clamps).
+which is an epilogue of the product kernels like SwiGLU (two accumulators); and ``weight_on_input``: a picked expert's
+weight multiplies its input, out = sum expert_e(w_e h), not its output (the two first products carry the weight as a
+factor, so the epilogue applies it to both sums in front of the clamps, in float32).
 
 The batched form lays the (token, slot) pairs out by expert, runs each expert over its
 tokens, and sums each token's pairs in slot order without atomics (the reference's
@@ -55,27 +55,21 @@ class DenseMlp(FeedForward):
         self.names = {**DENSE_NAMES, **(names or {})}
 
     def param_shapes(self):
-        if self.activation == "glu_clamp":
-            return {"w_gate_up": (2 * self.inter, self.hidden), "w_down": (self.hidden, self.inter)}
         s = {"w_up": (self.inter, self.hidden), "w_down": (self.hidden, self.inter)}
-        if self.activation == "swiglu":
+        if self.activation in ("swiglu", "glu_clamp"):
             s["w_gate"] = (self.inter, self.hidden)
         return s
 
     def sources(self):
         p, n = self.prefix, self.names
-        if self.activation == "glu_clamp":
-            return [TensorSource(f"{p}.{n['gate']}", (self.inter, self.hidden), "w_gate_up", 0),
-                    TensorSource(f"{p}.{n['up']}", (self.inter, self.hidden), "w_gate_up", self.inter),
-                    TensorSource(f"{p}.{n['down']}", (self.hidden, self.inter), "w_down")]
         out = [TensorSource(f"{p}.{n['up']}", (self.inter, self.hidden), "w_up"),
                TensorSource(f"{p}.{n['down']}", (self.hidden, self.inter), "w_down")]
-        if self.activation == "swiglu":
+        if self.activation in ("swiglu", "glu_clamp"):
             out.insert(0, TensorSource(f"{p}.{n['gate']}", (self.inter, self.hidden), "w_gate"))
         return out
 
     def kernel_modules(self, dtype):
-        return ["gemm_simt", "gemv", "elementwise"] + (["gemm_skinny", "gemm_tc"] if dtype == torch.bfloat16 else [])
+        return ["gemm_simt", "gemv"] + (["gemm_skinny", "gemm_tc"] if dtype == torch.bfloat16 else [])
 
     def forward(self, h, batch, residual, rt, row_scale=None, accumulate=True) -> None:
         self.forward_down(self.forward_up(h, rt), residual, rt, row_scale, accumulate)
@@ -87,9 +81,7 @@ class DenseMlp(FeedForward):
         if self.activation == "swiglu":
             K.linear(h, self.params["w_gate"], act, w2=self.params["w_up"])
         elif self.activation == "glu_clamp":
-            gu = rt.rows(f"dense_mlp.gu{2 * self.inter}", 2 * self.inter, torch.float32, h.shape[0])
-            K.linear(h, self.params["w_gate_up"], gu)
-            K.glu_clamp(gu, self.limit, act)
+            K.linear(h, self.params["w_gate"], act, w2=self.params["w_up"], act="glu_clamp", act_limit=self.limit)
         else:
             K.linear(h, self.params["w_up"], act, act="relu2")
         return act
@@ -184,13 +176,10 @@ class SparseMoe(FeedForward):
     def param_shapes(self):
         s = {
             "router": (self.R, self.hidden),
+            "up_exps": (self.E, self.I, self.hidden),
             "down_exps": (self.E, self.hidden, self.I),
         }
-        if self.activation == "glu_clamp":
-            s["gate_up_exps"] = (self.E, 2 * self.I, self.hidden)
-        else:
-            s["up_exps"] = (self.E, self.I, self.hidden)
-        if self.activation == "swiglu":
+        if self.activation in ("swiglu", "glu_clamp"):
             s["gate_exps"] = (self.E, self.I, self.hidden)
         if self.has_router_bias:
             s["router_bias"] = (self.R,)
@@ -204,13 +193,8 @@ class SparseMoe(FeedForward):
         p, n = self.prefix, self.names
         out = [TensorSource(f"{p}.{n['router']}", (self.R, self.hidden), "router")]
         for e in range(self.E):
-            if self.activation == "swiglu":
+            if self.activation in ("swiglu", "glu_clamp"):
                 out.append(TensorSource(f"{p}.{n['expert_gate'].format(e=e)}", (self.I, self.hidden), "gate_exps", e * self.I))
-            if self.activation == "glu_clamp":
-                out.append(TensorSource(f"{p}.{n['expert_gate'].format(e=e)}", (self.I, self.hidden), "gate_up_exps", 2 * e * self.I))
-                out.append(TensorSource(f"{p}.{n['expert_up'].format(e=e)}", (self.I, self.hidden), "gate_up_exps", (2 * e + 1) * self.I))
-                out.append(TensorSource(f"{p}.{n['expert_down'].format(e=e)}", (self.hidden, self.I), "down_exps", e * self.hidden))
-                continue
             out.append(TensorSource(f"{p}.{n['expert_up'].format(e=e)}", (self.I, self.hidden), "up_exps", e * self.I))
             out.append(TensorSource(f"{p}.{n['expert_down'].format(e=e)}", (self.hidden, self.I), "down_exps",
                                     e * self.hidden))
@@ -253,16 +237,13 @@ class SparseMoe(FeedForward):
             # router rows and the gate row as one matrix (a copy of a few hundred KB)
             self._router_all = torch.cat([r, g.view(1, -1)], 0).contiguous() if g is not None else r
 
-    def _first_product(self, x, act, rt=None, scale=None, **kw) -> None:
+    def _first_product(self, x, act, scale=None, **kw) -> None:
         """``scale`` = (weights, the pairs' order): the picks' weights as a factor on the experts' input."""
         if self.activation == "swiglu":
             K.linear(x, self.params["gate_exps"], act, w2=self.params["up_exps"], **kw)
         elif self.activation == "glu_clamp":
-            n = kw["n_rows"]
-            gu = rt.rows(f"moe.gu{2 * self.I}", 2 * self.I, torch.float32, n, per_token=self.k)
-            K.linear(x, self.params["gate_up_exps"], gu, **kw)
-            K.glu_clamp(gu, self.limit, act, n_rows=n, row_scale=scale[0] if scale else None,
-                        scale_rows=scale[1] if scale else None)
+            K.linear(x, self.params["gate_exps"], act, w2=self.params["up_exps"], act="glu_clamp", act_limit=self.limit,
+                     row_scale=scale[0] if scale else None, scale_rows=scale[1] if scale else None, **kw)
         else:
             K.linear(x, self.params["up_exps"], act, act="relu2", **kw)
 
@@ -278,9 +259,8 @@ class SparseMoe(FeedForward):
         # which kernels the expert products run on decides the row tile of the expert layout
         tile = K.FEW_ROWS if T <= K.FEW_ROWS else K.expert_tile(n_pairs, self.E)
         widths_ok = self.I % 8 == 0 and self.hidden % 8 == 0
-        first_w = self.params["gate_up_exps" if self.activation == "glu_clamp" else "up_exps"]
         on_input = (wts, lay.sorted_pair) if self.weight_on_input else None
-        all_bf16 = (K.tensor_cores_take(h, first_w) and widths_ok
+        all_bf16 = (K.tensor_cores_take(h, self.params["up_exps"]) and widths_ok
                     and self.params["down_exps"].dtype == torch.bfloat16)
         if not all_bf16 and widths_ok and n_pairs <= K.FEW_ROWS * self.E:
             # No tensor-core form (float32) and a handful of rows per expert: tiles of 8 rows on the row-streaming
@@ -344,13 +324,13 @@ class SparseMoe(FeedForward):
             K.moe_identity(h, wts, lay, pair_out, n_pairs=n_pairs, top_k=self.k, n_real=self.E)
         if streamed or not all_bf16:
             # few rows per expert (or no tensor-core form): the kernels gather the token rows themselves
-            self._first_product(h, act, rt=rt, scale=on_input, x_rows=lay.sorted_pair, x_row_div=self.k, layout=lay,
+            self._first_product(h, act, scale=on_input, x_rows=lay.sorted_pair, x_row_div=self.k, layout=lay,
                                 n_rows=n_pairs)
         else:
             # tcgen05 kernel: TMA reads whole row ranges, so lay the tokens out in expert order first
             xs = rt.rows("moe.x_sorted", self.hidden, rt.dtype, n_pairs, per_token=self.k)
             K.gather_rows(h, lay.sorted_pair, self.k, xs, n_pairs)
-            self._first_product(xs, act, rt=rt, scale=on_input, layout=lay, n_rows=n_pairs)
+            self._first_product(xs, act, scale=on_input, layout=lay, n_rows=n_pairs)
         K.linear(act, self.params["down_exps"], pair_out, layout=lay, n_rows=n_pairs,
                  row_scale=None if self.weight_on_input else wts,
                  scale_rows=None if self.weight_on_input else lay.sorted_pair, lists_ready=True, second_tiles=True)

@@ -9,7 +9,8 @@ head a state S [dim, v_dim] that is carried from token to token:
 Every head's o_t is RMS-normed over v_dim with one weight [v_dim] for all heads, the heads are concatenated, multiplied
 by silu(W_g h) and projected by W_o.  The state starts at zero, is float32, and lives in the request's state slot.  The
 projections are one product whose result stays float32, so that everything that enters the recurrence -- q, k, v, the
-decay's logits, sigmoid, root and the state -- is float32; the decay is formed as exp(-softplus(-z) / tau).
+decay's logits, sigmoid, root and the state -- is float32; the decay travels as 1 - a = -expm1(-softplus(-z) / tau), which
+keeps the rate of a slow channel (a within a few float32 spacings of 1) to float32's own precision.
 """
 from __future__ import annotations
 

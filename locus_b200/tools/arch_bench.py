@@ -1,9 +1,10 @@
-"""Prefill and decode throughput of the Lalepel, the Pozozen or the Mekizen design at layer sizes that resemble a real
-model's, beside the closest architecture at equal sizes (random weights, synthetic token ids, one GPU): Qwen2-MoE for
-Lalepel and Pozozen; for Mekizen both Pozozen (the closest mixers: windowed attention beside a float32 recurrence) and
-Qwen2-MoE.
+"""Prefill and decode throughput of the Lalepel, the Pozozen, the Mekizen or the Gugozen design at layer sizes that
+resemble a real model's, beside the closest architecture at equal sizes (random weights, synthetic token ids, one GPU):
+Qwen2-MoE for Lalepel and Pozozen; for Mekizen both Pozozen (the closest mixers: windowed attention beside a float32
+recurrence) and Qwen2-MoE; for Gugozen both Lalepel (the closest mixers: latent attention and a float32 linear recurrence,
+with routed experts) and Qwen2-MoE.
 
-    python -m locus_b200.tools.arch_bench [--design lalepel|pozozen|mekizen] [--size m|s] [--layers 4] [--prefill 2048]
+    python -m locus_b200.tools.arch_bench [--design lalepel|pozozen|mekizen|gugozen] [--size m|s] [--layers 4] [--prefill 2048]
                                           [--batch 8] [--context 4096] [--steps 16] [--warmup 3] [--dtype bf16|fp32]
                                           [--kernels]
 
@@ -13,7 +14,9 @@ with routed experts; Pozozen's through (attention beside a state-space mixer, ma
 beside a state-space mixer) over two copies of the residual stream, with four identity experts beside the routed ones
 in eight (or four) groups of which half stay open; Mekizen's through (convolved attention beside a gated delta rule,
 windowed attention with kept first tokens and a sink, the same beside a delta rule again, attention on the second
-layer's keys and values), all with a dense squared-ReLU feed-forward of four times the width.  Timed on the device with CUDA events after warm-up; every step reads its weights (several
+layer's keys and values), all with a dense squared-ReLU feed-forward of four times the width; Gugozen's through
+(grouped-query attention with a learned sink, gated linear attention, latent attention, latent attention on the third
+layer's rows), all with clamped gated experts weighted on their input and a shared expert.  Timed on the device with CUDA events after warm-up; every step reads its weights (several
 hundred MB: more than the L2 holds).  ``--kernels`` adds, for one eager prefill step and one eager decode step of
 each model, the time by kernel entry point, and for the mixers' own kernels what their bytes or flops would take
 at the measured peaks.  Prints one JSON line.
@@ -87,6 +90,26 @@ def mekizen_config(z, n_layers):
             "embedding": {"scale": 1.0}, "layers": layers}
 
 
+def gugozen_config(z, n_layers):
+    moe = {"kind": "moe", "router": {"experts": z["experts"], "top": z["top"]}, "expert": {"ff": z["ff"], "limit": 7.0},
+           "shared": {"ff": z["shared"], "limit": 7.0}}
+    att = {"type": "attention", "mlp": moe, "mixer": {
+        "heads": z["heads"], "kv_heads": max(1, z["heads"] // 4), "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5,
+        "rot": {"base": 1000000.0, "dims": z["dim"] // 2}}}
+    rec = {"type": "gla", "mlp": moe, "mixer": {"heads": z["heads"], "dim": z["ret_dim"], "vdim": z["vdim"], "tau": 16.0}}
+
+    def lat(kv_from=None):
+        m = {"heads": z["heads"], "dim": z["dim"], "rot_dim": z["rot"], "vdim": z["vdim"], "kv_rank": z["kv_rank"],
+             "scale": (z["dim"] + z["rot"]) ** -0.5, "rot": {"base": 1000000.0, "dims": z["rot"]}}
+        if kv_from is not None:
+            m["kv_from"] = kv_from
+        return {"type": "latent_attention", "mlp": moe, "mixer": m}
+
+    layers = [(att, rec, lat(), lat(i - 1))[i % 4] if i % 4 != 3 else lat(i - 1) for i in range(n_layers)]
+    return {"architecture": "Gugozen", "width": z["width"], "vocab": z["vocab"], "norm": {"eps": 1e-5}, "postln_alpha": 2.0,
+            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 1000003, "mul_cur": 31}}, "layers": layers}
+
+
 def qwen_config(z, n_layers, max_pos):
     hd = z["dim"] + z["rot"] if (z["dim"] + z["rot"]) in (64, 128) else z["dim"]
     return {"architectures": ["Qwen2MoeForCausalLM"], "model_type": "qwen2_moe", "num_hidden_layers": n_layers,
@@ -129,10 +152,13 @@ def run(args) -> dict:
     pk = peaks()
     gen = torch.Generator().manual_seed(5)
     design = args.design
-    own = {"lalepel": lalepel_config, "pozozen": pozozen_config, "mekizen": mekizen_config}[design](z, args.layers)
+    own = {"lalepel": lalepel_config, "pozozen": pozozen_config, "mekizen": mekizen_config,
+           "gugozen": gugozen_config}[design](z, args.layers)
     raws = {design: own}
     if design == "mekizen":
         raws["pozozen"] = pozozen_config(z, args.layers)
+    if design == "gugozen":
+        raws["lalepel"] = lalepel_config(z, args.layers)
     raws["qwen2_moe"] = qwen_config(z, args.layers, max(ctx, T) + 8)
     raws["qwen2_moe"].pop("_head")
     out = {}
@@ -215,6 +241,26 @@ def run(args) -> dict:
     H, R = z["heads"], z["kv_rank"] + z["rot"]
     keys_avg = sum(min(p + 1, z["window"]) for p in range(T)) / T
     fma_tflops = 148 * 128 * 2 * 1.965e9 / 1e12       # float32 FMAs of the CUDA cores at the top clock
+    if design == "gugozen":
+        d, dv, G = z["ret_dim"], z["vdim"], max(1, H // 4)
+        bounds = {
+            "attn_prefill_us": 2.0 * T * (T + 1) / 2 * H * 2 * z["dim"] / (pk["bf16_tflops"] * 1e12) * 1e6,
+            "attn_decode_us": B * ctx * 2 * G * z["dim"] * el / (pk["hbm_gbs"] * 1e9) * 1e6,
+            # the absorbed form multiplies the cached row (latent and rotated part) per score and the latent per value
+            "latent_attn_prefill_us": 2.0 * T * (T + 1) / 2 * H * (R + z["kv_rank"]) / (pk["bf16_tflops"] * 1e12) * 1e6,
+            "latent_attn_decode_us": B * ctx * R * el / (pk["hbm_gbs"] * 1e9) * 1e6,
+            # per token and head the decayed rank-one update and the read-out, float32 FMAs
+            "gla_prefill_us": 2.0 * T * H * 2 * d * dv / (fma_tflops * 1e12) * 1e6,
+            "gla_decode_us": B * H * d * dv * 4 * 2 / (pk["hbm_gbs"] * 1e9) * 1e6,
+            "retention_decode_us": B * H * d * dv * 4 * 2 / (pk["hbm_gbs"] * 1e9) * 1e6,
+            "qwen_attn_decode_us": B * ctx * 2 * H * z["dim"] * el / (pk["hbm_gbs"] * 1e9) * 1e6,
+            "fp32_fma_tflops": fma_tflops,
+        }
+        return {"metric": f"prefill and decode tokens/s, Gugozen beside Lalepel and Qwen2-MoE at equal layer sizes "
+                          f"({args.size}, {args.layers} layers, {args.dtype})",
+                "size": z, "layers": args.layers, "dtype": args.dtype, "data": "synthetic", "designs": out,
+                "bounds_per_layer": bounds, "peaks": pk,
+                "l2": "no flush: every step reads its weights, more than the 126 MB L2"}
     if design == "mekizen":
         d, dv = z["ret_dim"], z["vdim"]
         chan = 2 * H * d + H * dv
@@ -278,7 +324,7 @@ def run(args) -> dict:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="arch_bench", description=__doc__.split("\n\n")[0])
-    ap.add_argument("--design", default="lalepel", choices=["lalepel", "pozozen", "mekizen"])
+    ap.add_argument("--design", default="lalepel", choices=["lalepel", "pozozen", "mekizen", "gugozen"])
     ap.add_argument("--size", default="m", choices=sorted(SIZES))
     ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--prefill", type=int, default=2048)

@@ -49,11 +49,25 @@ class ExpertLayout(K.ExpertLayout):
 
 def linear(x, w, out, *, w2=None, bias=None, accumulate=False, row_scale=None, scale_rows=None, x_rows=None, lists_ready=False,
            second_tiles=False,
-           x_row_div=1, layout=None, n_rows=None, act=None):
-    assert act in (None, "relu2") and not (act and w2 is not None)
+           x_row_div=1, layout=None, n_rows=None, act=None, act_limit=0.0):
+    assert act in (None, "relu2", "glu_clamp") and not (act == "relu2" and w2 is not None)
+    assert act != "glu_clamp" or (w2 is not None and act_limit > 0)
     M = out.shape[0] if n_rows is None else n_rows
     if M == 0:
         return
+    rs_all = None
+    if row_scale is not None:
+        rs_all = _f(row_scale[scale_rows[:M].long()] if scale_rows is not None else row_scale[:M])[:, None]
+
+    def unit(g, u, rows):
+        """Two products of the same rows into one: SwiGLU, or the clamped gated unit with the rows' scale in front."""
+        if act != "glu_clamp":
+            return g / (1.0 + torch.exp(-g)) * u
+        s = rs_all[rows] if rs_all is not None else 1.0
+        g = torch.clamp(g * s, max=act_limit)
+        u = torch.clamp(u * s, min=-act_limit, max=act_limit)
+        return g / (1.0 + torch.exp(-1.702 * g)) * (u + 1.0)
+
     if x_rows is not None:
         xin = _f(x)[(x_rows[:M].long() // x_row_div)]
     else:
@@ -61,8 +75,7 @@ def linear(x, w, out, *, w2=None, bias=None, accumulate=False, row_scale=None, s
     if layout is None:
         y = xin @ _f(w).T
         if w2 is not None:
-            u = xin @ _f(w2).T
-            y = y / (1.0 + torch.exp(-y)) * u
+            y = unit(y, xin @ _f(w2).T, slice(0, M))
     else:
         y = torch.zeros(M, w.shape[1], dtype=xin.dtype)
         off = layout.offsets.tolist()
@@ -71,15 +84,14 @@ def linear(x, w, out, *, w2=None, bias=None, accumulate=False, row_scale=None, s
             if b > a:
                 ye = xin[a:b] @ _f(w[e]).T
                 if w2 is not None:
-                    ye = ye / (1.0 + torch.exp(-ye)) * (xin[a:b] @ _f(w2[e]).T)
+                    ye = unit(ye, xin[a:b] @ _f(w2[e]).T, slice(a, b))
                 y[a:b] = ye
     if bias is not None:
         y = y + _f(bias)
     if act == "relu2":
         y = torch.clamp(y, min=0.0) ** 2
-    if row_scale is not None:
-        rs = row_scale[scale_rows[:M].long()] if scale_rows is not None else row_scale[:M]
-        y = y * _f(rs)[:, None]
+    if rs_all is not None and act != "glu_clamp":
+        y = y * rs_all
     if layout is not None:
         M = min(M, int(layout.offsets[w.shape[0]]))   # a grouped product writes the rows of its experts only
         y = y[:M]
@@ -184,6 +196,8 @@ def _select(logits_row, top_k, renorm, scale, score_fn, sel_bias, n_group, n_gro
     else:
         p = 1.0 / (1.0 + torch.exp(-r))
     sel = p.clone() if sel_bias is None else p + sel_bias.to(p.dtype).cpu()
+    if score_fn == "sigmoid" and sel_bias is None and n_group <= 1:
+        sel = r.clone()     # ranked by the logits: the same order, no ties where the sigmoid rounds to one score
     sel = torch.where(torch.isnan(sel), torch.full_like(sel, -3.0e38), sel)
     if n_group > 1:
         per = E // n_group
@@ -511,21 +525,9 @@ def span_rmsnorm(x, spans, eps):
         x[:, off:off + n] = (v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps) * _f(w)).to(x.dtype)
 
 
-def glu_clamp(gu, limit, out, *, n_rows=None, row_scale=None, scale_rows=None):
-    n = out.shape[0] if n_rows is None else n_rows
-    inter = out.shape[1]
-    s = 1.0
-    if row_scale is not None:
-        idx = scale_rows[:n].long() if scale_rows is not None else torch.arange(n)
-        s = _f(row_scale)[idx][:, None]
-    g = torch.clamp(_f(gu[:n, :inter]) * s, max=limit)
-    u = torch.clamp(_f(gu[:n, inter:2 * inter]) * s, min=-limit, max=limit)
-    out[:n] = (g / (1.0 + torch.exp(-1.702 * g)) * (u + 1.0)).to(out.dtype)
-
-
 def gla_decay(z, off, n, tau):
     v = _f(z[:, off:off + n])
-    z[:, off:off + n] = torch.exp(-torch.nn.functional.softplus(-v) / tau).to(z.dtype)
+    z[:, off:off + n] = (-torch.expm1(-torch.nn.functional.softplus(-v) / tau)).to(z.dtype)
 
 
 def gla_scan(q, off_q, k, off_k, v, off_v, decay, off_a, state, state_offset, state_slots, seg_q0, seg_qn, n_seg, out, *,
@@ -540,7 +542,7 @@ def gla_scan(q, off_q, k, off_k, v, off_v, decay, off_a, state, state_offset, st
             kv = _f(k[r, off_k:off_k + H * d]).view(H, d)
             av = _f(decay[r, off_a:off_a + H * d]).view(H, d)
             vv = _f(v[r, off_v:off_v + H * dv]).view(H, dv)
-            S = av[:, :, None] * S + kv[:, :, None] * vv[:, None, :]
+            S = (S - av[:, :, None] * S) + kv[:, :, None] * vv[:, None, :]
             out[r] = (torch.einsum("hdv,hd->hv", S, qv) * q_scale).reshape(-1).to(out.dtype)
         state[slot, state_offset:state_offset + H * d * dv] = S.reshape(-1).to(state.dtype)
 
@@ -751,7 +753,7 @@ _NAMES = ["embed_rows", "rmsnorm", "rmsnorm_adds", "attn_chunk_tc_takes", "linea
           "cast_rows", "rmsnorm_add", "latent_prep", "latent_q_split", "latent_attn", "heads_to_rows", "retention_scan",
           "retention_gate_norm", "head_tile", "latent_attn_mma_takes", "layernorm", "stream_update", "moe_identity",
           "gated_recurrence", "mlstm_gates", "mlstm_out", "ssm_conv", "ssm_out", "head_prep", "gate_rows", "delta_rule", "delta_out",
-          "embed_pair", "layernorm_post", "span_rmsnorm", "glu_clamp", "gla_decay", "gla_scan"]
+          "embed_pair", "layernorm_post", "span_rmsnorm", "gla_decay", "gla_scan"]
 
 
 def install(monkeypatch) -> None:

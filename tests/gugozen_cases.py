@@ -175,34 +175,36 @@ class Case:
 
     def ref_following(self, rid, routed, near_tie):
         """The plain logits when the plain implementation takes the engine's picks (``routed``: prefix -> {position:
-        picks}) where they differ from its own.  A difference is allowed only at a near-tie: every expert the engine
-        picked must have a router logit within ``near_tie`` times the spread of the token's logits of the plain
-        implementation's weakest own pick."""
-        base, aux = self.ref(rid)
-        T = len(self.tokens[rid])
-        forced, differs = {}, 0
-        for prefix, per_pos in (routed or {}).items():
-            z = aux[prefix]
-            top = len(next(iter(per_pos.values()))) if per_pos else 0
-            own = torch.topk(z, top, dim=-1).indices if top else None
-            rows = []
-            for pos in range(T):
-                mine = own[pos].tolist()
-                eng = per_pos.get(pos, mine)
-                if sorted(eng) != sorted(mine):
-                    differs += 1
-                    weakest = min(float(z[pos, e]) for e in mine)
-                    spread = float(z[pos].max() - z[pos].min())
-                    for e in eng:
-                        assert float(z[pos, e]) >= weakest - near_tie * spread, (
-                            f"{self.name}/{rid} {prefix} position {pos}: the engine picked expert {e} with logit "
-                            f"{float(z[pos, e]):.5f}; the plain implementation's weakest pick has {weakest:.5f}")
-                rows.append(eng)
-            forced[int(prefix.split(".")[0][1:])] = rows
-        if differs == 0:
-            return base
-        # the picks of later layers were made by the engine on its own activations: follow them all
-        return self.ref(rid, picks=forced)[0]
+        picks}) where they differ from its own, layer by layer, so that every layer's scores are those of the activations
+        that the picks before it gave.  A difference is allowed only at a near-tie: every expert the engine picked must
+        have a score within ``near_tie`` times the spread of the token's scores (at least 0.25: two experts that lie close
+        have none) of the plain implementation's weakest own pick."""
+        if not routed:
+            return self.ref(rid)[0]
+        name = self.name
+
+        def follow(prefix, per_pos):
+            def choose(logits):
+                z = torch.sigmoid(logits)
+                top = len(next(iter(per_pos.values())))
+                own = torch.topk(logits, top, dim=-1).indices
+                rows = []
+                for pos in range(z.shape[0]):
+                    mine = own[pos].tolist()
+                    eng = per_pos.get(pos, mine)
+                    if sorted(eng) != sorted(mine) and near_tie is not None:
+                        weakest = min(float(z[pos, e]) for e in mine)
+                        spread = max(float(z[pos].max() - z[pos].min()), 0.25)
+                        for e in eng:
+                            assert float(z[pos, e]) >= weakest - near_tie * spread, (
+                                f"{name}/{rid} {prefix} position {pos}: the engine picked expert {e} with score "
+                                f"{float(z[pos, e]):.5f}; the plain implementation's weakest pick has {weakest:.5f}")
+                    rows.append(eng)
+                return rows
+            return choose
+
+        forced = {int(prefix.split(".")[0][1:]): follow(prefix, per_pos) for prefix, per_pos in routed.items() if per_pos}
+        return plain.forward(self.cfg, self.weights, self.tokens[rid], picks=forced)[0]
 
 
 def errors(out, ref):
@@ -222,6 +224,20 @@ def compare(case, got, routed, tol_max, tol_mean, near_tie):
         worst = int(err.argmax())
         assert float(err.max()) <= tol_max, f"{case.name}/{rid}: position {worst} is off by {float(err.max()):.2e} of the largest logit"
         assert mean <= tol_mean, f"{case.name}/{rid}: mean error {mean:.2e}"
+
+
+def compare_together(case, got, routed, tol_max, tol_mean, one_in=10, cap=5.0):
+    """As ``compare``, for bfloat16 models in which single positions amplify the rounding of the activations (sharp
+    softmaxes over scores of tens, five or six post-norm layers on top of each other): the engine's picks are followed
+    without judging them, all but one row in ``one_in`` lie within ``tol_max``, none beyond ``cap`` times that, and the
+    mean error is held.  The kernels' plain twins with bfloat16 buffers are off in such rows by as much."""
+    for rid, out in got.items():
+        ref = case.ref_following(rid, routed.get(rid), None)
+        assert out.shape == ref.shape and bool(torch.isfinite(out).all()), rid
+        err, mean = errors(out, ref)
+        assert mean <= tol_mean, f"{case.name}/{rid}: mean error {mean:.2e}"
+        assert float(err.max()) <= cap * tol_max, f"{case.name}/{rid}: position {int(err.argmax())} is off by {float(err.max()):.2e}"
+        assert int((err > tol_max).sum()) <= max(1, len(err) // one_in), f"{case.name}/{rid}: {int((err > tol_max).sum())} rows beyond {tol_max}"
 
 
 def random_config(seed):

@@ -159,12 +159,14 @@ def route(weights, pre, h, top):
 
 
 def moe_ff(f, weights, pre, h, picks=None):
-    """``picks``: the experts to use per token (a list of lists of expert numbers) instead of the router's own choice;
-    the weights are always the router's scores."""
+    """``picks``: the experts to use per token (a list of lists of expert numbers, or a function of the router's logits
+    [T, experts] that returns one) instead of the router's own choice; the weights are always the router's scores."""
     T = h.shape[0]
     out = torch.zeros_like(h)
     chosen = route(weights, pre, h, f["router"]["top"])
     if picks is not None:
+        if callable(picks):
+            picks = picks(h @ _w(weights, pre + "router").T)
         s = torch.sigmoid(h @ _w(weights, pre + "router").T)
         chosen = [[(e, s[t, e]) for e in picks[t]] for t in range(T)]
     for t in range(T):
