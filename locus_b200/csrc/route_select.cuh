@@ -62,7 +62,7 @@ __device__ __forceinline__ void select_token(const float* __restrict__ lg, float
     const bool by_logit = (o.score_fn & SCORE_FN_MASK) == SCORE_SIGMOID && o.sel_bias == nullptr && o.n_group <= 1;
     for (int x = lane; x < E; x += 32) {
         const float v = by_logit ? __ldcg(lg + x) : p[x] + (o.sel_bias != nullptr ? o.sel_bias[x] : 0.f);
-        sel[x] = (v == v) ? v : -3.0e38f;
+        sel[x] = (v == v) ? fmaxf(v, -3.0e38f) : -3.0e38f;   // (a logit of -inf still ranks above an expert already taken)
     }
     __syncwarp();
     if (o.n_group > 1) {

@@ -5,7 +5,7 @@
     python -m locus_b200.tools.kernel_bench attn_chunk --tokens 2048 --ctx 0
     python -m locus_b200.tools.kernel_bench experts --tokens 2048 [--experts 60 --top-k 4 --k 2048 --n 1408] [--part up|down]
     python -m locus_b200.tools.kernel_bench recurrence --tokens 2048 --batch 1 [--heads 16 --head-dim 128 --v-dim 128]
-                                                       [--per-group 1] [--ones] [--retention | --delta]
+                                                       [--per-group 1] [--ones] [--retention | --delta | --gla]
     python -m locus_b200.tools.kernel_bench head_prep --tokens 2048 --batch 1 [--window 4096]
 
 Times with CUDA events after warm-up.  Weights rotate through enough copies that the L2
@@ -216,6 +216,8 @@ def bench_recurrence(args) -> None:
     slots = torch.arange(B, dtype=torch.int32, device=dev)
     if args.delta:
         return _bench_delta(args, B, n, H, d, dv, G, q0, qn, slots, g)
+    if args.gla:
+        return _bench_gla(args, B, n, H, d, dv, q0, qn, slots, g)
     if args.retention:
         rows = (torch.randn(T, 2 * H * d + 2 * H * dv, generator=g) * 0.3).to(dev)
         state = torch.zeros(B, H, d, dv, device=dev)
@@ -241,6 +243,25 @@ def bench_recurrence(args) -> None:
     by = 4.0 * (2 * B * H * d * dvx + rows.numel() + out.numel())
     fl = 2.0 * T * H * ((32 * d + 32 * dvx if n >= 16 else 0) + 2 * d * dvx)
     print(f"{'retention' if args.retention else 'gated recurrence'}: {B} x {n} tokens, {H} heads of {d} x {dvx}: {us:.1f} us/call, "
+          f"{fl / us / 1e6:.2f} TFLOP/s (float32 FMA), {by / us / 1e3:.0f} GB/s")
+
+
+def _bench_gla(args, B, n, H, d, dv, q0, qn, slots, g) -> None:
+    """Gated linear attention at the same sizes: a decay per key channel near 1 (given as 1 - decay).  FLOPs: the decayed
+    rank-one update and S^T q per token and head; bytes: the states read and written, the operands, the outputs."""
+    dev, T = "cuda:0", B * n
+    rows = (torch.randn(T, 2 * H * d + H * dv, generator=g) * 0.3).to(dev)
+    lose = (torch.rand(T, H * d, generator=g) * 0.1).to(dev)
+    state = torch.zeros(B, H * d * dv, device=dev)
+    out = torch.zeros(T, H * dv, device=dev)
+
+    def fn():
+        K.gla_scan(rows, 0, rows, H * d, rows, 2 * H * d, lose, 0, state, 0, slots, q0, qn, B, out, n_heads=H, dim=d,
+                   v_dim=dv, q_scale=d ** -0.5)
+    us = _time(fn, args.iters, args.graph)
+    by = 4.0 * (2 * B * H * d * dv + rows.numel() + lose.numel() + out.numel())
+    fl = 2.0 * T * H * 2 * d * dv
+    print(f"gated linear attention: {B} x {n} tokens, {H} heads of {d} x {dv}: {us:.1f} us/call, "
           f"{fl / us / 1e6:.2f} TFLOP/s (float32 FMA), {by / us / 1e3:.0f} GB/s")
 
 
@@ -357,6 +378,7 @@ def main(argv=None) -> int:
     ap.add_argument("--ones", action="store_true", help="recurrence: one column more, whose v is 1")
     ap.add_argument("--retention", action="store_true", help="recurrence: the fixed-decay kernels instead")
     ap.add_argument("--delta", action="store_true", help="recurrence: the gated delta rule instead")
+    ap.add_argument("--gla", action="store_true", help="recurrence: gated linear attention (a decay per key channel) instead")
     ap.add_argument("--page-tokens", type=int, default=64)
     ap.add_argument("--window", type=int, default=0)
     ap.add_argument("--keep-first", type=int, default=0, dest="keep_first",

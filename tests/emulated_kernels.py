@@ -198,7 +198,7 @@ def _select(logits_row, top_k, renorm, scale, score_fn, sel_bias, n_group, n_gro
     sel = p.clone() if sel_bias is None else p + sel_bias.to(p.dtype).cpu()
     if score_fn == "sigmoid" and sel_bias is None and n_group <= 1:
         sel = r.clone()     # ranked by the logits: the same order, no ties where the sigmoid rounds to one score
-    sel = torch.where(torch.isnan(sel), torch.full_like(sel, -3.0e38), sel)
+    sel = torch.clamp(torch.where(torch.isnan(sel), torch.full_like(sel, -3.0e38), sel), min=-3.0e38)
     if n_group > 1:
         per = E // n_group
         gs = []

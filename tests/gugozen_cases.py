@@ -96,9 +96,12 @@ SEEDS = {n: 171 + i for i, n in enumerate(CONFIGS)}
 DECAY_RANKS = {"mix": {1: 5, 3: 16}, "odd": {1: 3}, "gla_only": {0: 8}}
 
 
-def sharpen(name, w):
-    """Weights (name -> float32 tensor) changed in place so that far keys, sinks, states, clamps and the router matter."""
+def sharpen(name, w, strength=1.0):
+    """Weights (name -> float32 tensor) changed in place so that far keys, sinks, states, clamps and the router matter.
+    ``strength`` < 1 moves the factors on the projections towards 1 (deep bfloat16 models, whose rounding sharp scores
+    amplify)."""
     g = torch.Generator().manual_seed(9)
+    f = lambda m: 1.0 + (m - 1.0) * strength
     for layer, rank in DECAY_RANKS.get(name, {}).items():
         a1, a2 = w[f"l{layer}.mix.a1"], w[f"l{layer}.mix.a2"]
         w[f"l{layer}.mix.a1"] = torch.randn(rank, a1.shape[1], generator=g) * 0.02
@@ -110,11 +113,13 @@ def sharpen(name, w):
         elif n.endswith((".norm1.b", ".norm2.b")) or n == "final.norm.b":
             w[n] = (torch.rand(t.shape, generator=g) - 0.5) * 0.4
         elif n.endswith((".mix.q", ".mix.k", ".mix.dkv", ".mix.uk")):
-            w[n] = t * 12.0                                                 # scores spread over several units
+            # scores spread over several units, whatever the width (scores of tens turn every rounding of a layer's
+            # input into ten times as much behind its softmax)
+            w[n] = t * f(12.0 * min(1.0, (64.0 / t.shape[1]) ** 0.5))
         elif n.endswith((".mix.v", ".mix.uv", ".mix.o")):
-            w[n] = t * 5.0
+            w[n] = t * f(5.0)
         elif n.endswith(".mix.g"):
-            w[n] = t * 8.0
+            w[n] = t * f(8.0)
         elif n.endswith(".mix.sink"):
             w[n] = torch.linspace(-1.0, 2.0, t.numel())                      # sinks that compete with the keys
         elif n.endswith(".mix.a1"):
@@ -124,9 +129,9 @@ def sharpen(name, w):
         elif n.endswith(".mix.a2.b"):
             w[n] = torch.linspace(-3.0, 6.0, t.numel())                      # channels from fast to slow
         elif n.endswith(".router"):
-            w[n] = t * 25.0                                                  # scores from near 0 to near 1
+            w[n] = t * f(25.0)                                               # scores from near 0 to near 1
         elif n.endswith((".gate", ".up")):
-            w[n] = t * 15.0                                                  # the clamps are reached
+            w[n] = t * f(15.0)                                               # the clamps are reached
         elif n.endswith(".down"):
             w[n] = t * 4.0
         elif n in ("embed", "bigram"):

@@ -60,18 +60,21 @@ def test_drawn_configurations_on_pages_of_64(seed, dtype, tmp_path_factory):
     """Configurations drawn at random (layer order, head counts and sizes, rotated parts, latents and layers on other
     layers' latents, decays, experts, constants): portions of changing size and mixed batches of four live requests on
     pages of 64 whose pool only holds them when pages are used again."""
+    import functools
+
     raw = random_config(300 + seed)
+    # (sharp scores in five to seven post-norm layers amplify the rounding of bfloat16 activations: milder factors there)
+    tweak = sharpen if dtype == torch.float32 else functools.partial(sharpen, strength=0.4)
     case = Case(f"drawn{seed}", tmp_path_factory.mktemp("drawn"), torch.bfloat16, raw=raw, requests=(230, 1, 150, 40, 97, 180),
-                seed=seed)
+                seed=seed, tweak=tweak)
     runner, cache = make_runner(case, dtype, DEV, page_tokens=64, n_pages=14, max_tokens=256, max_seq=512)
     sch = schedules(case)
     for name in ("mixed", "chunked"):
         got, routed = run_steps(runner, cache, case, sch[name])
         if dtype == torch.bfloat16:
-            # sharpened weights in five to seven post-norm layers amplify the rounding of bfloat16 activations
             compare_together(case, got, routed, 0.1, 1.5e-2, one_in=10, cap=3.0)
         else:
-            compare(case, got, routed, *TOL[dtype], NEAR_TIE[dtype])
+            compare(case, got, routed, 2e-4, 4e-5, NEAR_TIE[dtype])   # (five to seven sharpened layers deep)
         assert cache.free_pages() == cache.total_pages()
 
 
@@ -163,7 +166,7 @@ def test_gla_scan_and_decay_against_twin(H, d, dv, precise):
     import locus_b200.kernels as K
 
     g = torch.Generator().manual_seed(H * 100 + d)
-    qn = [1, 37, 2, 16]
+    qn = [1, 37, 2, 100]
     T = sum(qn)
     W = 2 * H * d + H * dv + 4   # (the parts need not start on 16-byte boundaries)
     proj = torch.randn(T, W, generator=g)
@@ -172,8 +175,9 @@ def test_gla_scan_and_decay_against_twin(H, d, dv, precise):
     z[0, 0], z[1, 1] = 40.0, -40.0           # decays of 1 and of (nearly) 0
     state = torch.randn(5, H * d * dv + 7, generator=g)
     slots = torch.tensor([3, 0, 4, 1], dtype=torch.int32)
-    q0 = torch.tensor([0, 1, 38, 40], dtype=torch.int32)
+    q0 = torch.tensor([0, 1, 38, 40], dtype=torch.int32)   # (the segments' first rows)
     n = torch.tensor(qn, dtype=torch.int32)
+
     for tau in (1.0, 16.0):
         ref_z, ref_state, ref_out = z.clone().double(), state.clone().double(), torch.zeros(T, H * dv, dtype=torch.float64)
         EK.gla_decay(ref_z, 0, H * d, tau)
@@ -190,6 +194,12 @@ def test_gla_scan_and_decay_against_twin(H, d, dv, precise):
         rest = n - first
         K.gla_scan(dp, off_q, dp, off_k, dp, off_v, dz, 0, ds, 7, slots.to(DEV), (q0 + first).to(DEV), rest.to(DEV), 4, out,
                    n_heads=H, dim=d, v_dim=dv, q_scale=d ** -0.5)
+        # and whole, from the same start
+        ds2, out2 = state.to(DEV), torch.zeros(T, H * dv, device=DEV)
+        K.gla_scan(dp, off_q, dp, off_k, dp, off_v, dz, 0, ds2, 7, slots.to(DEV), q0.to(DEV), n.to(DEV), 4, out2,
+                   n_heads=H, dim=d, v_dim=dv, q_scale=d ** -0.5)
+        _cmp(out2, ref_out, 2e-5)
+        _cmp(ds2, ref_state, 2e-5)
         _cmp(out, ref_out, 2e-5)
         _cmp(ds, ref_state, 2e-5)
 

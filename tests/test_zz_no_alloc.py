@@ -57,7 +57,7 @@ def _call(lib, static, c, out, nh, nkv, hd, P, window, max_splits, scratch=None)
     part_o, part_ml, counters = scratch
     units = min(part_o.numel() // hd, part_ml.numel() // 2)
     return lib.locus_attn_decode(*head, p(part_o), p(part_ml), p(counters), I(max_splits), ctypes.c_longlong(units),
-                                 I(0), I(0), stream)     # (no kept first tokens, no sink)
+                                 I(0), I(0), None, stream)     # (no kept first tokens, no sink, no learned sink)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
