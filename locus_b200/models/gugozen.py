@@ -92,7 +92,7 @@ def build_plan(cfg: GugozenConfig, tensor_shapes=None) -> ModelPlan:
 
 
 # the width of a gla layer's first decay projection where no stored tensor says it (random-weights mode)
-DECAY_RANK = 16
+DECAY_RANK = 32
 
 register_arch(ArchEntry(
     name="Gugozen",

@@ -82,18 +82,18 @@ CONFIGS = {
     "latent_only": model(48, 50, [with_mlp(latent(2, 16, 8, 16, 24), 0), with_mlp(latent(4, 8, 8, 8, 24, kv_from=0), 0)],
                          bigram=None),
     "moe_only": model(48, 50, [with_mlp(gla(1, 8, 8, tau=2.0), 8, 2, 16, 1.0, shared=(24, 1.5))], bigram=(17, 3, 7)),
-    # larger heads: heads of 128 with values of 80 (the kernels' head size above the values'), rows of the recurrence
+    # larger heads: heads of 128 with values of 96 (the kernels' head size above the values'), rows of the recurrence
     # beyond a lane's first registers, a latent of 64 + 16 on the tensor-core kernel's sizes
     "wide": model(128, 211, [
-        with_mlp(attention(4, 2, 128, 80, rot=32, base=1e6, scale=0.09), 8, 2, 32, 1.5, shared=(64, 2.0)),
-        with_mlp(gla(2, 72, 40, tau=16.0), 8, 1, 32, 1.5),
-        with_mlp(latent(4, 32, 16, 32, 64, scale=0.14), 4, 1, 64, 1.5, shared=(32, 2.0)),
+        with_mlp(attention(4, 2, 128, 96, rot=48, base=5e5, scale=0.09), 8, 2, 32, 1.75, shared=(64, 2.5)),
+        with_mlp(gla(2, 72, 40, tau=12.0), 8, 1, 32, 1.75),
+        with_mlp(latent(4, 32, 16, 32, 64, scale=0.14), 4, 1, 48, 1.25, shared=(32, 2.5)),
         with_mlp(latent(2, 32, 16, 48, 64, kv_from=2, scale=0.14), 0),
-    ], alpha=3.0, bigram=(257, 127, 7)),
+    ], alpha=3.0, bigram=(257, 113, 9)),
 }
 SEEDS = {n: 171 + i for i, n in enumerate(CONFIGS)}
 # other widths of a gla layer's first decay projection than the random-weights mode draws (configuration -> layer -> rows)
-DECAY_RANKS = {"mix": {1: 5, 3: 16}, "odd": {1: 3}, "gla_only": {0: 8}}
+DECAY_RANKS = {"mix": {1: 5, 3: 12}, "odd": {1: 3}, "gla_only": {0: 8}}
 
 
 def sharpen(name, w, strength=1.0):
@@ -277,5 +277,5 @@ def random_config(seed):
                          r.choice([32, 64, 96, 128]), scale=round(r.uniform(0.05, 0.3), 3), base=r.choice([1e4, 1e6]))
             owners.append(i)
         layers.append(with_mlp(lay, experts, min(top, experts or 1), r.choice([16, 32, 64]), r.choice([1.0, 1.5, 3.0]), shared))
-    bigram = r.choice([None, (r.choice([101, 509, 1021]), r.choice([3, 127, 1000003]), r.choice([1, 7, 65537]))])
+    bigram = r.choice([None, (r.choice([101, 509, 2039]), r.choice([3, 131, 1000003]), r.choice([1, 11, 65537]))])
     return model(width, r.randint(100, 700), layers, eps=r.choice([1e-5, 1e-6]), alpha=r.choice([1.0, 2.0, 2.5, 4.0]), bigram=bigram)

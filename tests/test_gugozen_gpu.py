@@ -96,13 +96,13 @@ def test_other_page_sizes_and_the_cuda_core_products(page_tokens, dtype, cases, 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
 def test_heads_of_128_in_long_portions_on_pages_of_64(dtype, tmp_path_factory):
-    """Heads of 128 with values of 80 and three query heads on every key/value head, portions of several hundred tokens
+    """Heads of 128 with values of 96 and four query heads on every key/value head, portions of several hundred tokens
     (the attention kernels that long portions of that head size take, with the learned sink), a recurrence whose state
     has 128 rows, a latent layer on another one's rows, pages of 64."""
-    raw = model(256, 301, [with_mlp(attention(6, 2, 128, 80, rot=32, base=1e6, scale=0.09), 8, 2, 64, 1.5, shared=(128, 2.0)),
-                           with_mlp(gla(2, 128, 64, tau=16.0), 0),
-                           with_mlp(latent(4, 64, 16, 64, 128, scale=0.11), 8, 1, 64, 1.5),
-                           with_mlp(latent(4, 64, 16, 64, 128, kv_from=2, scale=0.11), 0)], alpha=2.5, bigram=(1021, 127, 7))
+    raw = model(256, 301, [with_mlp(attention(8, 2, 128, 96, rot=64, base=5e5, scale=0.1), 8, 2, 96, 1.75, shared=(160, 2.5)),
+                           with_mlp(gla(2, 128, 64, tau=12.0), 0),
+                           with_mlp(latent(4, 64, 32, 48, 128, scale=0.11), 8, 1, 96, 1.75),
+                           with_mlp(latent(4, 64, 32, 48, 128, kv_from=2, scale=0.11), 0)], alpha=3.0, bigram=(997, 131, 11))
     case = Case("big", tmp_path_factory.mktemp("big"), torch.bfloat16, raw=raw, requests=(700, 90))
     runner, cache = make_runner(case, dtype, DEV, page_tokens=64, n_pages=20, max_tokens=640, max_seq=1024)
     steps = [[("r0", 300), ("r1", 40)], [("r0", 399), ("r1", 1)], [("r0", 1), ("r1", 49)]]

@@ -82,7 +82,7 @@ def test_plan_shares_rows_between_layers_and_gives_the_embedding_a_slot(tmp_path
     # the width of a gla layer's first decay projection comes from the stored tensor's shape
     case = Case("mix", tmp_path, torch.float32)
     loaded = load_model(case.dir, torch.float32, "cpu")
-    assert loaded.blocks[1].mixer.rank == 5 and loaded.blocks[3].mixer.rank == 16
+    assert loaded.blocks[1].mixer.rank == 5 and loaded.blocks[3].mixer.rank == 12
     assert tuple(case.weights["l1.mix.a1"].shape) == (5, 64)
 
 
