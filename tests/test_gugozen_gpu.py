@@ -292,6 +292,113 @@ def test_the_clamped_gated_unit_on_every_product_kernel(M, tc, dtype, precise, m
         K.linear(x.to(DEV), w.to(DEV), out, act="glu_clamp", act_limit=lim)
 
 
+@pytest.mark.parametrize("nh,nkv,hd,dtype", [(6, 2, 128, torch.bfloat16), (8, 2, 64, torch.bfloat16), (2, 2, 128, torch.bfloat16),
+                                             (3, 1, 96, torch.bfloat16), (4, 2, 64, torch.float32)],
+                         ids=["6on2_128", "8on2_64", "2on2_128", "3on1_96", "f32_4on2_64"])
+def test_every_attention_kernel_with_a_learned_sink(nh, nkv, hd, dtype):
+    """A learned score per query head in the softmax's denominator, from far below the keys' scores to above them:
+    the portion kernels (tcgen05 whole and with its keys cut into ranges, mma.sync, CUDA cores) and the decode kernels
+    (streaming per head and per group of query heads in both variants, fixed ranges) against the twin in float64, a
+    batch and requests alone; the sink is not multiplied by the scores' factor."""
+    import locus_b200.kernels as K
+    from test_mekizen_gpu import _close, _paged_attention_case
+
+    P = 64
+    sink = torch.linspace(-3.0, 2.5, nh)
+    tol = 1.5e-2 if dtype == torch.bfloat16 else 2e-5
+    # portions
+    segs = [(0, 5), (33, 17), (100, 2), (64, 64), (190, 130), (600, 70)]
+    pool, q, meta, T = _paged_attention_case(dtype, nh, nkv, hd, P, segs, 0, 0, seed=nh + hd)
+    kw = dict(n_heads=nh, n_kv_heads=nkv, head_dim=hd, page_tokens=P, window=0, scale=0.11)
+    items64 = torch.tensor([(s, o) for s, (c, n) in enumerate(segs) for o in range(0, n, K.MMA_QUERY_TILE)], dtype=torch.int32)
+    items16 = torch.tensor([(s, o) for s, (c, n) in enumerate(segs) for o in range(0, n, 16)], dtype=torch.int32)
+    ref = torch.zeros(T, nh * hd, dtype=torch.float64)
+    EK.PRECISE = True
+    try:
+        EK.attn_chunk(q, pool, ref, items=items16, n_items=len(items16), sink=sink, **meta, **kw)
+        plain_ref = torch.zeros(T, nh * hd, dtype=torch.float64)
+        EK.attn_chunk(q, pool, plain_ref, items=items16, n_items=len(items16), sink=True, **meta, **kw)
+    finally:
+        EK.PRECISE = False
+    assert not _close(plain_ref, ref, 10 * tol)     # (a sink of score 0 in its place is far away)
+    dev = {k: v.cuda() for k, v in meta.items()}
+    dsink = sink.cuda()
+
+    def fresh():
+        return torch.full((T, nh * hd), float("nan"), dtype=dtype, device="cuda")
+
+    if K.attn_chunk_tc_takes(q.cuda(), hd, P, T, 2048):
+        out = fresh()
+        K.attn_chunk_tc(q.cuda(), pool.cuda(), out, items=items64.cuda(), n_items=len(items64), sink=dsink, **dev, **kw)
+        assert K.attn_tc_error() == 0 and _close(out, ref, tol), "attn_chunk_tc"
+        for n_splits in (2, 7):
+            part_o = torch.full((T * nh * n_splits * hd,), float("nan"), device="cuda")
+            part_ml = torch.full((T * nh * n_splits * 2,), float("nan"), device="cuda")
+            out = fresh()
+            K.attn_chunk_tc(q.cuda(), pool.cuda(), out, items=items64.cuda(), n_items=len(items64), n_splits=n_splits,
+                            part_o=part_o, part_ml=part_ml, sink=dsink, **dev, **kw)
+            assert K.attn_tc_error() == 0 and _close(out, ref, tol), f"attn_chunk_tc in {n_splits} key ranges"
+    if K.attn_chunk_mma_takes(q.cuda(), hd):
+        out = fresh()
+        K.attn_chunk_mma(q.cuda(), pool.cuda(), out, items=items64.cuda(), n_items=len(items64), sink=dsink, **dev, **kw)
+        assert _close(out, ref, tol), "attn_chunk_mma"
+        n_o, n_ml = K.attn_chunk_mma_scratch(hd)
+        part_o, part_ml = torch.full((n_o,), float("nan"), device="cuda"), torch.full((n_ml,), float("nan"), device="cuda")
+        some = items64[-2:]     # (the last request's tiles, behind 600 keys, cut into ranges)
+        out = fresh()
+        K.attn_chunk_mma(q.cuda(), pool.cuda(), out, items=some.cuda(), n_items=len(some), n_splits=4, part_o=part_o,
+                         part_ml=part_ml, sink=dsink, **dev, **kw)
+        lo = int(meta["seg_q0"][-1])
+        assert _close(out[lo:], ref[lo:], tol), "attn_chunk_mma in 4 key ranges"
+    out = fresh()
+    K.attn_chunk(q.cuda(), pool.cuda(), out, items=items16.cuda(), n_items=len(items16), sink=dsink, **dev, **kw)
+    assert _close(out, ref, tol), "attn_chunk"
+    # single tokens
+    ctxs = [0, 1, 31, 32, 33, 63, 64, 100, 130, 200, 263, 333, 461, 700, 1023, 1100]
+    segs = [(c, 1) for c in ctxs]
+    pool, q, meta, T = _paged_attention_case(dtype, nh, nkv, hd, P, segs, 0, 0, seed=nh + hd + 1)
+    items = torch.arange(len(segs), dtype=torch.int32)
+    ref = torch.zeros(T, nh * hd, dtype=torch.float64)
+    EK.PRECISE = True
+    try:
+        EK.attn_chunk(q, pool, ref, items=torch.stack([items, torch.zeros_like(items)], 1), n_items=len(items), sink=sink, **meta, **kw)
+    finally:
+        EK.PRECISE = False
+    dev = {k: v.cuda() for k, v in meta.items()}
+    max_splits = (max(ctxs) // K.DECODE_SPLIT) + 1
+    units = K.decode_units(len(segs), nh, hd, dtype, max_splits, "cuda", page_tokens=P, n_kv_heads=nkv)
+    part_o = torch.full((units * hd,), float("nan"), device="cuda")
+    part_ml = torch.full((units * 2,), float("nan"), device="cuda")
+    counters = torch.zeros(len(segs) * nh, dtype=torch.int32, device="cuda")
+    use_gqa, ran_gqa = K.USE_GQA_DECODE, False
+    try:
+        for gqa, deep in [(g, d) for g in (True, False) for d in (None, True, False)]:
+            if gqa and not K.attn_decode_gqa_takes(dtype, nh, nkv, hd, P, len(segs)):
+                continue
+            ran_gqa = ran_gqa or gqa
+            K.USE_GQA_DECODE = gqa
+            K.attn_decode_variant(deep)
+            K.attn_decode_gqa_variant(deep)
+            what = f"{'grouped' if gqa else 'per head'}, variant {deep}"
+            out = fresh()
+            K.attn_decode(q.cuda(), pool.cuda(), out, items=items.cuda(), n_items=len(items), part_o=part_o, part_ml=part_ml,
+                          counters=counters, max_splits=max_splits, sink=dsink, **dev, **kw)
+            assert K.attn_error() == 0 and K.attn_gqa_error() == 0
+            assert _close(out, ref, tol), what
+            assert int(counters.abs().sum()) == 0
+            for lo, hi in ((5, 6), (len(segs) - 1, len(segs)), (len(segs) - 16, len(segs))):
+                one = fresh()
+                K.attn_decode(q.cuda(), pool.cuda(), one, items=items[lo:hi].cuda(), n_items=hi - lo, part_o=part_o,
+                              part_ml=part_ml, counters=counters, max_splits=max_splits, sink=dsink, **dev, **kw)
+                assert _close(one[lo:hi], ref[lo:hi], tol), f"{what}, requests {lo} to {hi} alone"
+    finally:
+        K.USE_GQA_DECODE = use_gqa
+        K.attn_decode_variant(None)
+        K.attn_decode_gqa_variant(None)
+    if dtype == torch.bfloat16 and nh != nkv and hd in (64, 128):
+        assert ran_gqa, "the grouped decode kernel did not take this shape"
+
+
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
 def test_a_far_key_among_hundreds_in_a_prompt_and_in_decoding(dtype, tmp_path_factory):
     """One early token whose embedding is scaled up draws the attention of every later query (softmax and latent
